@@ -68,6 +68,10 @@ class ModelSpec:
     # Regular expressions of tensor names that a checkpoint may hold and the
     # model does not use (they are not reported as unexpected).
     ignored_tensors: Tuple[str, ...] = ()
+    # What runs of the schedule start with (a part of the "run_input" family that owns a table), and where:
+    # (run number, entry of the table, whether the embedding's output is added to the stream too).
+    run_input: Optional[PartSpec] = None
+    run_input_at: Tuple[Tuple[int, int, bool], ...] = ()
 
     def validate(self) -> None:
         n = len(self.layers)
@@ -76,6 +80,11 @@ class ModelSpec:
         for i in self.schedule:
             if not 0 <= i < n:
                 raise ValueError(f"ModelSpec.schedule names layer {i}, but there are {n} layers")
+        if self.run_input_at and self.run_input is None:
+            raise ValueError("ModelSpec.run_input_at without a run_input part")
+        for run, _, _ in self.run_input_at:
+            if not 0 <= run < len(self.schedule):
+                raise ValueError(f"ModelSpec.run_input_at names run {run}, but the schedule has {len(self.schedule)}")
         for i, layer in enumerate(self.layers):
             if layer.cache_of is not None:
                 j = layer.cache_of

@@ -222,13 +222,25 @@ __device__ __forceinline__ void softmax_block(float (&s)[NKT][4], float (&o)[HD 
 }
 
 // ------------------------------------------------------------------- prefill
+// With a sink (one more term exp(sink) in a row's denominator) the factor that turns a row's accumulated
+// sum_j exp2(s_j - m) v_j into its result: 1 / (l + exp2(sink log2e - m)), written so that a sink far above the
+// largest score does not overflow.  m and l are the row's running maximum (in log2 units) and sum.
+__device__ __forceinline__ float sink_inverse(float m, float l, float sink) {
+    const float sk = sink * LOG2E;
+    if (m == -INFINITY) return 0.f;
+    if (sk <= m) return 1.f / (l + exp2f(sk - m));
+    const float c = exp2f(m - sk);
+    return c / (fmaf(l, c, 1.f));
+}
+
 constexpr int PF_STAGES = 2;
 constexpr size_t PF_SMEM = (size_t)(1 + 2 * PF_STAGES) * TILE_ELEMS * sizeof(bf16);
 
 __global__ void __launch_bounds__(NT)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                     bf16* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_kv_len,
-                    const int* __restrict__ block_table, int max_pages, int H, int G, float scale_log2, int window) {
+                    const int* __restrict__ block_table, int max_pages, int H, int G, float scale_log2, int window,
+                    const float* __restrict__ sink) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_s = q_s + TILE_ELEMS;                     // [PF_STAGES][64][LDS]
@@ -312,7 +324,12 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     }
     cp_wait<0>();
 
-    const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    if (sink) {
+        // one more term exp(sink[head]) in the denominator (no key, no value, not scaled)
+        if (r_lo < rows_total) inv_lo = sink_inverse(m[0], l[0], sink[g * R + r_lo % R]);
+        if (r_hi < rows_total) inv_hi = sink_inverse(m[1], l[1], sink[g * R + r_hi % R]);
+    }
 #pragma unroll
     for (int hi = 0; hi < 2; ++hi) {
         const int grow = hi ? r_hi : r_lo;
@@ -392,7 +409,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
                    bf16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                    int max_pages, int H, int G, float scale_log2, int window, int row_groups, const Rotary rot,
-                   int q_rows, const __grid_constant__ PageMaps maps, int* __restrict__ status) {
+                   int q_rows, const __grid_constant__ PageMaps maps, int* __restrict__ status,
+                   const float* __restrict__ sink) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const size_t q_bytes = (size_t)q_rows * LDS * sizeof(bf16);          // q_rows: 16, or 9 (8 heads and a row of zeros)
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
@@ -623,7 +641,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
                 result[r * (HD + 2) + HD + 1] = ll;
             }
         } else if (n_splits == 1) {
-            out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+            out[row * HD + d] = __float2bfloat16_rn(sink ? acc * sink_inverse(mm, ll, sink[h0 + r]) : ll > 0.f ? acc / ll : 0.f);
         } else {
             ws_o[(row * n_splits + split) * HD + d] = acc;
             if (d == 0) {
@@ -662,7 +680,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
                 acc += wgt * as[sp];
                 ll += wgt * ls[sp];
             }
-            out[((size_t)t * H + h0 + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+            out[((size_t)t * H + h0 + r) * HD + d] =
+                __float2bfloat16_rn(sink ? acc * sink_inverse(mm, ll, sink[h0 + r]) : ll > 0.f ? acc / ll : 0.f);
         }
         cluster_sync_all();                             // nobody reads this CTA's shared memory any more
     }
@@ -677,7 +696,8 @@ constexpr int MERGE_MAX_SPLITS = 8192;                   // the weights of all r
 constexpr int MERGE_LANES = HD <= 64 ? 64 : HD <= 128 ? 128 : 256;
 constexpr int MERGE_GROUPS = MERGE_THREADS / MERGE_LANES;
 __global__ void __launch_bounds__(MERGE_THREADS)
-attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int n_splits) {
+attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, bf16* __restrict__ out, int n_splits,
+                  const float* __restrict__ sink, int H) {
     extern __shared__ float merge_w[];                  // [n_splits] weights, then [MERGE_GROUPS][MERGE_LANES] sums
     __shared__ float red[MERGE_THREADS / 32];
     __shared__ float s_max, s_l;
@@ -735,7 +755,7 @@ attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_m
         float total = sums[d];
         for (int k = 1; k < MERGE_GROUPS; ++k) total += sums[k * MERGE_LANES + d];
         const float ll = s_l;
-        out[row * HD + d] = __float2bfloat16_rn(ll > 0.f ? total / ll : 0.f);
+        out[row * HD + d] = __float2bfloat16_rn(sink ? total * sink_inverse(mm, ll, sink[row % H]) : ll > 0.f ? total / ll : 0.f);
     }
 }
 
@@ -768,7 +788,7 @@ extern "C" int plm_attn_head_dim() { return HD; }
 // max_new is the largest number of new tokens of a sequence.
 extern "C" int plm_attn_prefill(const void* q, const void* kc, const void* vc, void* out, const int* seq_start,
                                 const int* seq_kv_len, const int* block_table, int max_pages, int n_seqs, int max_new,
-                                int H, int G, float scale, int window, cudaStream_t stream) {
+                                int H, int G, float scale, int window, const float* sink, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_seqs > 65535 || G > 65535) return PLM_ERR_SHAPE;
     static bool configured = false;
@@ -781,7 +801,7 @@ extern "C" int plm_attn_prefill(const void* q, const void* kc, const void* vc, v
     dim3 grid(((size_t)max_new * R + 63) / 64, G, n_seqs);
     return plm_status_of(launch_pdl(attn_prefill_kernel, grid, dim3(NT), PF_SMEM, stream, (const bf16*)q, (const bf16*)kc,
                                     (const bf16*)vc, (bf16*)out, seq_start, seq_kv_len, block_table, max_pages, H, G,
-                                    scale * LOG2E, window));
+                                    scale * LOG2E, window, sink));
 }
 
 // Floats of workspace that plm_attn_decode needs for (tokens, H, splits): acc then (m, l).
@@ -797,7 +817,7 @@ extern "C" long plm_attn_decode_workspace(int n_tokens, int H, int n_splits) {
 extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, void* out, float* workspace,
                                const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
                                int n_tokens, int H, int G, float scale, int window, int n_splits, int n_pages,
-                               int* status, cudaStream_t stream) {
+                               int* status, const float* sink, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_splits < 1 || n_tokens > 65535) return PLM_ERR_SHAPE;
     constexpr bool TMA = HAS_TMA;
@@ -825,17 +845,17 @@ extern "C" int plm_attn_decode(const void* q, const void* kc, const void* vc, vo
         return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, false, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status, sink));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
     int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, false, TMA>, grid, dim3(NT), smem, stream, (const bf16*)q,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, Rotary{}, q_rows, maps, status, sink));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(MERGE_THREADS),
                                     (size_t)(n_splits + MERGE_THREADS) * sizeof(float), stream,
-                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
+                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits, sink, H));
 }
 
 // Decode with the rotary encoding and the cache write folded in (see struct Rotary): qkv [T, (H + 2G) * HD]
@@ -873,15 +893,15 @@ extern "C" int plm_attn_decode_rope(const void* qkv, void* kc, void* vc, void* o
         return plm_status_of(launch_pdl_cluster(attn_decode_kernel<true, true, TMA>, grid, dim3(NT), dim3(n_splits, 1, 1), smem,
                                                 stream, (const bf16*)qkv, (const bf16*)kc, (const bf16*)vc, (bf16*)out,
                                                 (float*)nullptr, (float*)nullptr, tok_pos, tok_seq, block_table,
-                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status));
+                                                max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status, (const float*)nullptr));
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * HD : nullptr;
     int rc = plm_status_of(launch_pdl(attn_decode_kernel<false, true, TMA>, grid, dim3(NT), smem, stream, (const bf16*)qkv,
                                       (const bf16*)kc, (const bf16*)vc, (bf16*)out, ws_o, ws_ml, tok_pos, tok_seq,
-                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status));
+                                      block_table, max_pages, H, G, scale * LOG2E, window, row_groups, rot, q_rows, maps, status, (const float*)nullptr));
     if (rc != PLM_OK || n_splits == 1) return rc;
     return plm_status_of(launch_pdl(attn_merge_kernel, dim3(n_tokens * H), dim3(MERGE_THREADS),
                                     (size_t)(n_splits + MERGE_THREADS) * sizeof(float), stream,
-                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits));
+                                    (const float*)ws_o, (const float*)ws_ml, (bf16*)out, n_splits, (const float*)nullptr, H));
 }

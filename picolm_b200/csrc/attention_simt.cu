@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const Tc* __restrict__ vc,
                       Ta* __restrict__ out, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                       const int* __restrict__ block_table, int max_pages, int H, int G, int hd, float scale,
-                      int window) {
+                      int window, const float* __restrict__ sink) {
     extern __shared__ float q_sm[];                 // [WARPS][hd]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -78,6 +78,14 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
         }
         m = m_new;
     }
+    if (sink) {
+        // a sink: one more term exp(sink[h]) in the denominator, with no key and no value, not scaled
+        const float sk = sink[h], m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= corr;
+    }
     const float inv = 1.0f / l;
     Ta* o = out + ((size_t)t * H + h) * hd;
 #pragma unroll
@@ -93,7 +101,8 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
 // both are PLM_F32 or both PLM_BF16.
 extern "C" int plm_attention_rows(const void* q, const void* kc, const void* vc, void* out, int dtype,
                                   const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
-                                  int n_tokens, int H, int G, int hd, float scale, int window, cudaStream_t stream) {
+                                  int n_tokens, int H, int G, int hd, float scale, int window, const float* sink,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || hd <= 0 || hd > MAX_HD) return PLM_ERR_SHAPE;
     dim3 grid(n_tokens, (H + WARPS - 1) / WARPS);
@@ -101,7 +110,7 @@ extern "C" int plm_attention_rows(const void* q, const void* kc, const void* vc,
 #define ROWS_LAUNCH(Ta_, MAXHD_)                                                                                       \
     attention_rows_kernel<Ta_, Ta_, MAXHD_><<<grid, WARPS * 32, smem, stream>>>(                                       \
         (const Ta_*)q, (const Ta_*)kc, (const Ta_*)vc, (Ta_*)out, tok_pos, tok_seq, block_table, max_pages, H, G, hd, \
-        scale, window)
+        scale, window, sink)
 #define ROWS_BY_SIZE(Ta_)                          \
     do {                                           \
         if (hd <= 256) ROWS_LAUNCH(Ta_, 256);      \

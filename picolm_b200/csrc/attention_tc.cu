@@ -165,7 +165,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_kv_len,
                        const int* __restrict__ block_table, int max_pages, int H, int G, float scale_log2, int window,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, const float* __restrict__ sink) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -440,7 +440,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc_fence_after();
         if (!ok) s_abort = 1;
         if (ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (sink && m_ref != -INFINITY) {
+                // one more term exp(sink[h]) in the denominator (no key, no value, not scaled); l counts from m_ref,
+                // and the form is chosen so that a sink far above the scores does not overflow
+                const float sk = sink[h] * LOG2E;
+                if (sk <= m_ref) inv = 1.f / (l + exp2f(sk - m_ref));
+                else { const float c = exp2f(m_ref - sk); inv = c / fmaf(l, c, 1.f); }
+            }
             bf16* dst = out + ((size_t)(t0 + tile * BQ + r) * H + h) * HD;
 #pragma unroll
             for (int c = 0; c < HD; c += 32) {
@@ -489,7 +496,7 @@ extern "C" int plm_attn_tc_trace_read(void* host_out) {
 extern "C" int plm_attn_tc_prefill(const void* q, const void* kc, const void* vc, void* out, const int* seq_start,
                                    const int* seq_kv_len, const int* block_table, int max_pages, int n_pages,
                                    int n_tokens, int n_seqs, int max_new, int H, int G, float scale, int window,
-                                   int* status, cudaStream_t stream) {
+                                   int* status, const float* sink, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0 || n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || H % G || n_seqs > 65535 || H > 65535) return PLM_ERR_SHAPE;
     if ((((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out)) & 15) return PLM_ERR_ALIGN;
@@ -506,5 +513,5 @@ extern "C" int plm_attn_tc_prefill(const void* q, const void* kc, const void* vc
     if ((rc = make_map(&mv, vc, (long)n_pages * G * BKV, HD, HD, BKV)) != PLM_OK) return rc;
     dim3 grid((max_new + BQ - 1) / BQ, H, n_seqs);
     return plm_status_of(launch_pdl(attn_tc_prefill_kernel, grid, dim3(NUM_THREADS), SMEM, stream, mq, mk, mv, (bf16*)out,
-                                    seq_start, seq_kv_len, block_table, max_pages, H, G, scale * LOG2E, window, status));
+                                    seq_start, seq_kv_len, block_table, max_pages, H, G, scale * LOG2E, window, status, sink));
 }

@@ -688,13 +688,14 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
                           Tc* __restrict__ vc, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                           const int* __restrict__ block_table, int max_pages, int H, int G, int D, int Dv, int hd_c,
-                          int rot_dim, int pairing, int own_kv) {
+                          int rot_dim, int pairing, int own_kv, int per_head, int v_from_k) {
     extern __shared__ float qk_sm[];                 // [nq + nk]
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int nq = H * D, nk = own_kv ? G * D : 0, nv = own_kv ? G * Dv : 0;
+    // v_from_k: there is no value projection; the keys as projected (with their bias, before norm and rotation) are the values
+    const int nq = H * D, nk = own_kv ? G * D : 0, nv = own_kv && !v_from_k ? G * Dv : 0;
     const int pos = PLM_POSITION(tok_pos[t]);
     const Ta* row = qkv + (size_t)t * (nq + nk + nv);
     float sq = 0.f, sk = 0.f;
@@ -705,11 +706,12 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
         if (i < nq) sq += v * v; else sk += v * v;
     }
     sq = block_sum<NT>(sq, red);
-    const float rq = wq ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
+    // per_head: the root mean square is taken over each head's own D columns (below), the weight [D] serves every head
+    const float rq = wq && !per_head ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
     float rk = 1.0f;
     if (nk > 0) {
         sk = block_sum<NT>(sk, red);
-        if (wk) rk = 1.0f / sqrtf(sk / (float)nk + eps);
+        if (wk && !per_head) rk = 1.0f / sqrtf(sk / (float)nk + eps);
     }
     size_t page_base = 0;
     int in_page = 0;
@@ -732,8 +734,13 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
         const int hh = is_q ? head : head - H;
         const float* src = qk_sm + (is_q ? 0 : nq) + hh * D;
         const Tw* wn = is_q ? wq : wk;
-        if (wn) wn += hh * D;
-        const float r = is_q ? rq : rk;
+        if (wn && !per_head) wn += hh * D;
+        float r = is_q ? rq : rk;
+        if (wn && per_head) {
+            float ss = 0.f;
+            for (int j = lane; j < D; j += 32) ss = fmaf(src[j], src[j], ss);
+            r = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+        }
         Tc* o;
         if (is_q) {
             o = q_out + ((size_t)t * H + hh) * hd_c;
@@ -769,7 +776,9 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
         for (int item = threadIdx.x; item < G * hd_c; item += NT) {
             const int g = item / hd_c, c = item - g * hd_c;
             float v = 0.f;
-            if (c < Dv) {
+            if (v_from_k) {
+                if (c < D) v = qk_sm[nq + g * D + c];
+            } else if (c < Dv) {
                 v = to_f32<Ta>(row[nq + nk + g * Dv + c]);
                 if (bias) v += bias[nq + nk + g * Dv + c];
             }
@@ -783,7 +792,7 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
                                       float eps, void* q_out, void* kc, void* vc, int out_dtype, const float* cos_t,
                                       const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
                                       int max_pages, int n_tokens, int H, int G, int D, int Dv, int hd_c, int rot_dim,
-                                      int pairing, int own_kv, cudaStream_t stream) {
+                                      int pairing, int own_kv, int per_head, int v_from_k, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || hd_c < D || hd_c < Dv || (hd_c & 1) || rot_dim < 0 || rot_dim > D ||
         (rot_dim & 1))
@@ -798,11 +807,140 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
         return plm_status_of(launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
                                         (const Ta_*)qkv, bias, (const Tc_*)wq, (const Tc_*)wk, eps, (Tc_*)q_out, (Tc_*)kc, \
                                         (Tc_*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table, max_pages, H, G, D, Dv,  \
-                                        hd_c, rot_dim, pairing, own_kv));                                              \
+                                        hd_c, rot_dim, pairing, own_kv, per_head, v_from_k));                          \
     } while (0)
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_F32) QKN_LAUNCH(float, float);
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_BF16) QKN_LAUNCH(float, bf16);
     if (qkv_dtype == PLM_BF16 && out_dtype == PLM_BF16) QKN_LAUNCH(bf16, bf16);
 #undef QKN_LAUNCH
+    return PLM_ERR_DTYPE;
+}
+
+
+// ------------------------------------------------------------------------------------------------ Dynamic Tanh
+// A norm without statistics: out = tanh(alpha * v) * w + b, elementwise, v = x (+ delta (+ dbias)).  With `post_w`
+// the delta is first divided by its own root mean square (eps inside the root) and multiplied by post_w: a
+// sublayer's result that is normalised before it is added.  The sum is written back to x unless rows are gathered.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename To, int NT>
+__global__ void __launch_bounds__(NT)
+dyt_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ dbias,
+                const float* __restrict__ post_w, float post_eps, const float* __restrict__ extra,
+                const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b,
+                To* __restrict__ out, const int* __restrict__ rows, int d, int write_back) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = rows ? PLM_ROW_NO(rows[r]) : r;
+    float* xr = x + (size_t)src * d;
+    const float* dr = delta ? delta + (size_t)src * d : nullptr;
+    const float* er = extra ? extra + (size_t)src * d : nullptr;
+    float post = 1.0f;
+    if (dr && post_w) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < d; i += NT) ss = fmaf(dr[i], dr[i], ss);
+        post = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)d + post_eps);
+    }
+    const float a = alpha ? alpha[0] : 0.f;
+    To* o = out ? out + (size_t)r * d : nullptr;
+    for (int i = threadIdx.x; i < d; i += NT) {
+        float v = xr[i];
+        if (dr) v += post_w ? dr[i] * post * post_w[i] : dr[i];
+        if (dbias) v += dbias[i];
+        if (er) v += er[i];
+        if (write_back) xr[i] = v;
+        if (o) o[i] = from_f32<To>(alpha ? fmaf(tanhf(a * v), w[i], b[i]) : v);
+    }
+}
+
+// v = x + delta' + dbias + extra, in that order (every addend may be null; delta' is delta, or with `post_w` delta over
+// its root mean square times post_w).  The sum is written back to x unless `rows` gathers.  out (may be null) receives
+// tanh(alpha v) w + b, or v itself where alpha is null.
+extern "C" int plm_dyt_norm(float* x, const float* delta, const float* dbias, const float* post_w, float post_eps,
+                            const float* extra, const float* alpha, const float* w, const float* b, void* out, int out_dtype,
+                            const int* rows, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0) return PLM_ERR_SHAPE;
+    const int write_back = rows == nullptr && (delta != nullptr || dbias != nullptr || extra != nullptr);
+    if (out_dtype == PLM_F32)
+        return plm_status_of(launch_pdl(dyt_norm_kernel<float, 256>, dim3(n_rows), dim3(256), 0, stream, x, delta, dbias, post_w,
+                                        post_eps, extra, alpha, w, b, (float*)out, rows, d, write_back));
+    if (out_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(dyt_norm_kernel<bf16, 256>, dim3(n_rows), dim3(256), 0, stream, x, delta, dbias, post_w,
+                                        post_eps, extra, alpha, w, b, (bf16*)out, rows, d, write_back));
+    return PLM_ERR_DTYPE;
+}
+
+// x[r, :] += a[r, :] + b[r, :] + vec[:], in that order; every addend may be null.
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                                const float* __restrict__ vec, long n, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    if (a) v += a[i];
+    if (b) v += b[i];
+    if (vec) v += vec[i % d];
+    x[i] = v;
+}
+
+extern "C" int plm_add_rows(float* x, const float* a, const float* b, const float* vec, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    const long n = (long)n_rows * d;
+    return plm_status_of(launch_pdl(add_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, a, b, vec, n, d));
+}
+
+// out[r, :] = sa * (a[r, :] + bias_a[:]) + sb * b[r, :]: two float32 results added with two constants.
+__global__ void scaled_sum_kernel(const float* __restrict__ a, float sa, const float* __restrict__ bias_a,
+                                  const float* __restrict__ b, float sb, float* __restrict__ out, long n, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float va = a[i];
+    if (bias_a) va += bias_a[i % d];
+    out[i] = fmaf(sa, va, sb * b[i]);
+}
+
+extern "C" int plm_scaled_sum(const float* a, float sa, const float* bias_a, const float* b, float sb, float* out, int n_rows,
+                              int d, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    const long n = (long)n_rows * d;
+    return plm_status_of(launch_pdl(scaled_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, a, sa, bias_a, b,
+                                    sb, out, n, d));
+}
+
+// out[r, j] = gelu_tanh(gate[r, j]) * table[tok[row r], col0 + j]: a gate times a row of a per-token table.
+template <typename T, typename Tw>
+__global__ void token_gate_kernel(const T* __restrict__ gate, const Tw* __restrict__ table, long ld_table, int col0,
+                                  const int* __restrict__ tok, const int* __restrict__ rows, T* __restrict__ out, int n_rows,
+                                  int dim, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)n_rows * dim) return;
+    const int r = (int)(i / dim), j = (int)(i % dim);
+    int id = tok[rows ? PLM_ROW_NO(rows[r]) : r];
+    id = id < 0 ? 0 : id >= vocab ? vocab - 1 : id;
+    const float e = to_f32<Tw>(table[(long)id * ld_table + col0 + j]);
+    out[i] = from_f32<T>(gelu_tanh_f(to_f32<T>(gate[i])) * e);
+}
+
+extern "C" int plm_token_gate(const void* gate, int dtype, const void* table, int table_dtype, long ld_table, int col0,
+                              const int* tok, const int* rows, void* out, int n_rows, int dim, int vocab, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (dim <= 0 || vocab <= 0 || col0 < 0 || col0 + dim > ld_table) return PLM_ERR_SHAPE;
+    const dim3 grid((unsigned)(((long)n_rows * dim + 255) / 256));
+    if (dtype == PLM_F32 && table_dtype == PLM_F32)
+        return plm_status_of(launch_pdl(token_gate_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)gate,
+                                        (const float*)table, ld_table, col0, tok, rows, (float*)out, n_rows, dim, vocab));
+    if (dtype == PLM_BF16 && table_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(token_gate_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)gate,
+                                        (const bf16*)table, ld_table, col0, tok, rows, (bf16*)out, n_rows, dim, vocab));
     return PLM_ERR_DTYPE;
 }

@@ -49,11 +49,13 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // u [T, C] with row stride ldu; w [taps, C] (tap-major, so that neighbouring channels' weights are neighbours), the
 // last tap being the current token's; state [slot][taps - 1][C], oldest first.  One block row per token, one thread
 // per channel: inputs before the step's first token come from the state.
+#define CONV_ACT_SILU 0
+#define CONV_ACT_NONE 1
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ u, long ldu, const float* __restrict__ w, const float* __restrict__ bias,
                                    const float* __restrict__ state, long state_stride, const int* __restrict__ tok_seq,
                                    const int* __restrict__ seq_start, const int* __restrict__ seq_slot, T* __restrict__ out,
-                                   int n_tokens, int C, int taps) {
+                                   int n_tokens, int C, int taps, const float* __restrict__ in_bias, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -62,12 +64,13 @@ __global__ void causal_conv_kernel(const T* __restrict__ u, long ldu, const floa
     const int i = t - seq_start[b];
     const float* st = state + (long)seq_slot[b] * state_stride;
     float acc = bias ? bias[c] : 0.f;
+    const float ib = in_bias ? in_bias[c] : 0.f;     // added to the step's inputs; the state holds inputs with it
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j, li = i - back;
-        const float val = li >= 0 ? to_f32<T>(u[(long)(t - back) * ldu + c]) : st[(long)(taps - 1 + li) * C + c];
+        const float val = li >= 0 ? to_f32<T>(u[(long)(t - back) * ldu + c]) + ib : st[(long)(taps - 1 + li) * C + c];
         acc = fmaf(w[(long)j * C + c], val, acc);
     }
-    out[(long)t * C + c] = from_f32<T>(silu_f(acc));
+    out[(long)t * C + c] = from_f32<T>(act == CONV_ACT_SILU ? silu_f(acc) : acc);
 }
 
 // The same for bf16 rows whose channels come in eights on 16-byte boundaries: a thread takes 8 channels of a token
@@ -118,7 +121,7 @@ __global__ void causal_conv_vec8_kernel(const bf16* __restrict__ u, long ldu, co
 template <typename T>
 __global__ void causal_conv_state_kernel(const T* __restrict__ u, long ldu, float* __restrict__ state, long state_stride,
                                          const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int n_seqs,
-                                         int C, int taps) {
+                                         int C, int taps, const float* __restrict__ in_bias) {
     pdl_launch_dependents();
     pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -129,7 +132,7 @@ __global__ void causal_conv_state_kernel(const T* __restrict__ u, long ldu, floa
     // ascending s: slot s takes old slot s + n (> s), which no earlier iteration has overwritten
     for (int s = 0; s < taps - 1; ++s) {
         const int src = n - (taps - 1) + s;
-        st[(long)s * C + c] = src >= 0 ? to_f32<T>(u[(long)(t0 + src) * ldu + c]) : st[(long)(s + n) * C + c];
+        st[(long)s * C + c] = src >= 0 ? to_f32<T>(u[(long)(t0 + src) * ldu + c]) + (in_bias ? in_bias[c] : 0.f) : st[(long)(s + n) * C + c];
     }
 }
 
@@ -137,14 +140,15 @@ __global__ void causal_conv_state_kernel(const T* __restrict__ u, long ldu, floa
 template <typename T>
 __global__ void causal_conv_decode_kernel(const T* __restrict__ u, long ldu, const float* __restrict__ w,
                                           const float* __restrict__ bias, float* __restrict__ state, long state_stride,
-                                          const int* __restrict__ seq_slot, T* __restrict__ out, int n_seqs, int C, int taps) {
+                                          const int* __restrict__ seq_slot, T* __restrict__ out, int n_seqs, int C, int taps,
+                                          const float* __restrict__ in_bias, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)n_seqs * C) return;
     const int b = (int)(idx / C), c = (int)(idx % C);
     float* st = state + (long)seq_slot[b] * state_stride;
-    const float cur = to_f32<T>(u[(long)b * ldu + c]);
+    const float cur = to_f32<T>(u[(long)b * ldu + c]) + (in_bias ? in_bias[c] : 0.f);
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps - 1; ++j) {
         const float val = st[(long)j * C + c];
@@ -153,13 +157,14 @@ __global__ void causal_conv_decode_kernel(const T* __restrict__ u, long ldu, con
     }
     acc = fmaf(w[(long)(taps - 1) * C + c], cur, acc);
     if (taps > 1) st[(long)(taps - 2) * C + c] = cur;
-    out[(long)b * C + c] = from_f32<T>(silu_f(acc));
+    out[(long)b * C + c] = from_f32<T>(act == CONV_ACT_SILU ? silu_f(acc) : acc);
 }
 
 extern "C" int plm_causal_conv(const void* u, int dtype, long ldu, const float* w, const float* bias, float* state,
                                long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot, void* out,
-                               int n_tokens, int n_seqs, int C, int taps, int is_decode, cudaStream_t stream) {
-    if (n_tokens <= 0 || n_seqs <= 0 || C <= 0 || taps < 1) return PLM_ERR_SHAPE;
+                               int n_tokens, int n_seqs, int C, int taps, int is_decode, const float* in_bias, int act,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0 || C <= 0 || taps < 1 || (act != CONV_ACT_SILU && act != CONV_ACT_NONE)) return PLM_ERR_SHAPE;
     if (dtype != PLM_F32 && dtype != PLM_BF16) return PLM_ERR_DTYPE;
     const int nt = 256;
     cudaError_t e;
@@ -167,30 +172,30 @@ extern "C" int plm_causal_conv(const void* u, int dtype, long ldu, const float* 
         const unsigned grid = (unsigned)(((long)n_seqs * C + nt - 1) / nt);
         e = dtype == PLM_F32
                 ? launch_pdl(causal_conv_decode_kernel<float>, dim3(grid), dim3(nt), 0, stream, (const float*)u, ldu, w, bias, state,
-                             state_stride, seq_slot, (float*)out, n_seqs, C, taps)
+                             state_stride, seq_slot, (float*)out, n_seqs, C, taps, in_bias, act)
                 : launch_pdl(causal_conv_decode_kernel<bf16>, dim3(grid), dim3(nt), 0, stream, (const bf16*)u, ldu, w, bias, state,
-                             state_stride, seq_slot, (bf16*)out, n_seqs, C, taps);
+                             state_stride, seq_slot, (bf16*)out, n_seqs, C, taps, in_bias, act);
         return plm_status_of(e);
     }
     const dim3 grid((unsigned)n_tokens, (unsigned)((C + nt - 1) / nt));
-    if (dtype == PLM_BF16 && C % 8 == 0 && ldu % 8 == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0)
+    if (dtype == PLM_BF16 && in_bias == nullptr && act == CONV_ACT_SILU && C % 8 == 0 && ldu % 8 == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0)
         e = launch_pdl(causal_conv_vec8_kernel, dim3((unsigned)n_tokens, (unsigned)((C / 8 + 127) / 128)), dim3(128), 0, stream,
                        (const bf16*)u, ldu, w, bias, (const float*)state, state_stride, tok_seq, seq_start, seq_slot, (bf16*)out,
                        n_tokens, C, taps);
     else
     e = dtype == PLM_F32
             ? launch_pdl(causal_conv_kernel<float>, grid, dim3(nt), 0, stream, (const float*)u, ldu, w, bias, (const float*)state,
-                         state_stride, tok_seq, seq_start, seq_slot, (float*)out, n_tokens, C, taps)
+                         state_stride, tok_seq, seq_start, seq_slot, (float*)out, n_tokens, C, taps, in_bias, act)
             : launch_pdl(causal_conv_kernel<bf16>, grid, dim3(nt), 0, stream, (const bf16*)u, ldu, w, bias, (const float*)state,
-                         state_stride, tok_seq, seq_start, seq_slot, (bf16*)out, n_tokens, C, taps);
+                         state_stride, tok_seq, seq_start, seq_slot, (bf16*)out, n_tokens, C, taps, in_bias, act);
     if (e != cudaSuccess) return (int)e;
     if (taps == 1) return PLM_OK;
     const unsigned grid2 = (unsigned)(((long)n_seqs * C + nt - 1) / nt);
     e = dtype == PLM_F32
             ? launch_pdl(causal_conv_state_kernel<float>, dim3(grid2), dim3(nt), 0, stream, (const float*)u, ldu, state, state_stride,
-                         seq_start, seq_slot, n_seqs, C, taps)
+                         seq_start, seq_slot, n_seqs, C, taps, in_bias)
             : launch_pdl(causal_conv_state_kernel<bf16>, dim3(grid2), dim3(nt), 0, stream, (const bf16*)u, ldu, state, state_stride,
-                         seq_start, seq_slot, n_seqs, C, taps);
+                         seq_start, seq_slot, n_seqs, C, taps, in_bias);
     return plm_status_of(e);
 }
 
@@ -850,4 +855,351 @@ extern "C" int plm_store_rows_paged(const void* rows, int dtype, long ld, void* 
     else
         return PLM_ERR_DTYPE;
     return plm_status_of(e);
+}
+
+// ------------------------------------------------------------------------------------------------ gated diagonal recurrence
+// The real-gated linear recurrent unit: the channels come in `B` blocks of n; in block b
+//   zr = Wr[b] u_b + br,  zi = Wi[b] u_b + bi   (Wr[b], Wi[b] square, [out, in])
+//   log a = -sigmoid(zr) * rate,  a = exp(log a),  x = sqrt(1 - a^2) * sigmoid(zi) * u
+// with rate = 8 softplus(lambda) worked out once by the host.  1 - a^2 is taken as -expm1(2 log a), which keeps its
+// digits where a is close to 1.  The sums are fp32 and run over k in ascending order for every element.
+// One block: 32 tokens x 32 channels of one gate block, K in pieces of 32 through shared memory.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T, typename Tw>
+__global__ void __launch_bounds__(256)
+rglru_gates_kernel(const T* __restrict__ u, long ldu, const Tw* __restrict__ wr, const Tw* __restrict__ wi,
+                   const float* __restrict__ br, const float* __restrict__ bi, const float* __restrict__ rate,
+                   float* __restrict__ a_out, float* __restrict__ x_out, int n_tokens, int W, int n) {
+    __shared__ float us[32][33], wrs[32][33], wis[32][33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * 32, blk = blockIdx.y, o0 = blockIdx.z * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    float zr[4] = {0.f, 0.f, 0.f, 0.f}, zi[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < n; k0 += 32) {
+        const int kk = k0 + tx;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = ty + 8 * j, tt = t0 + row, oo = o0 + row;
+            us[row][tx] = (tt < n_tokens && kk < n) ? to_f32<T>(u[(long)tt * ldu + (long)blk * n + kk]) : 0.f;
+            const bool in = oo < n && kk < n;
+            const long at = ((long)blk * n + oo) * n + kk;
+            wrs[row][tx] = in ? to_f32<Tw>(wr[at]) : 0.f;
+            wis[row][tx] = in ? to_f32<Tw>(wi[at]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float a = wrs[tx][k], b = wis[tx][k];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float uv = us[ty + 8 * j][k];
+                zr[j] = fmaf(a, uv, zr[j]);
+                zi[j] = fmaf(b, uv, zi[j]);
+            }
+        }
+        __syncthreads();
+    }
+    const int o = o0 + tx;
+    if (o >= n) return;
+    const int c = blk * n + o;
+    const float b_r = br[c], b_i = bi[c], rt = rate[c];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int tt = t0 + ty + 8 * j;
+        if (tt >= n_tokens) continue;
+        const float uu = to_f32<T>(u[(long)tt * ldu + c]);
+        const float la = -sigmoid_f(zr[j] + b_r) * rt;
+        a_out[(long)tt * W + c] = expf(la);
+        x_out[(long)tt * W + c] = sqrtf(-expm1f(2.f * la)) * sigmoid_f(zi[j] + b_i) * uu;
+    }
+}
+
+extern "C" int plm_rglru_gates(const void* u, int dtype, long ldu, const void* wr, const void* wi, int w_dtype, const float* br,
+                               const float* bi, const float* rate, float* a_out, float* x_out, int n_tokens, int W, int blocks,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (W <= 0 || blocks <= 0 || W % blocks) return PLM_ERR_SHAPE;
+    const int n = W / blocks;
+    const dim3 grid((unsigned)((n_tokens + 31) / 32), (unsigned)blocks, (unsigned)((n + 31) / 32));
+    if (dtype == PLM_F32 && w_dtype == PLM_F32)
+        return plm_status_of(launch_pdl(rglru_gates_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)u, ldu,
+                                        (const float*)wr, (const float*)wi, br, bi, rate, a_out, x_out, n_tokens, W, n));
+    if (dtype == PLM_BF16 && w_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(rglru_gates_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)u, ldu,
+                                        (const bf16*)wr, (const bf16*)wi, br, bi, rate, a_out, x_out, n_tokens, W, n));
+    return PLM_ERR_DTYPE;
+}
+
+// S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens, out_t = S_t * gelu_tanh(y_t + y_bias).  One block
+// per (32 channels, sequence): its 32 warps take 32 equal stretches of the sequence's tokens; a first walk leaves each
+// stretch's product of decays and its own sum, one warp chains them from the cache's state, a second walk writes.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+diag_scan_kernel(const float* __restrict__ a, const float* __restrict__ x, const T* __restrict__ yraw, long ldy,
+                 const float* __restrict__ ybias, float* __restrict__ state, long state_stride, T* __restrict__ out,
+                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int W) {
+    __shared__ float As[32][33], Bs[32][33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y, lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    const int s0 = seq_start[b], s1 = seq_start[b + 1];
+    if (s1 <= s0) return;
+    const int L = (s1 - s0 + 31) / 32;
+    const int t0 = min(s1, s0 + seg * L), t1 = min(s1, t0 + L);
+    float A = 1.f, Bv = 0.f;
+    if (c < W)
+        for (int t = t0; t < t1; ++t) {
+            const float av = a[(long)t * W + c];
+            Bv = fmaf(av, Bv, x[(long)t * W + c]);
+            A *= av;
+        }
+    As[seg][lane] = A;
+    Bs[seg][lane] = Bv;
+    __syncthreads();
+    if (seg == 0 && c < W) {
+        float* st = state + (long)seq_slot[b] * state_stride;
+        float carry = st[c];
+        for (int s = 0; s < 32; ++s) {
+            const float sa = As[s][lane], sb = Bs[s][lane];
+            As[s][lane] = carry;
+            carry = fmaf(sa, carry, sb);
+        }
+        st[c] = carry;
+    }
+    __syncthreads();
+    if (c >= W) return;
+    float S = As[seg][lane];
+    const float yb = ybias ? ybias[c] : 0.f;
+    for (int t = t0; t < t1; ++t) {
+        S = fmaf(a[(long)t * W + c], S, x[(long)t * W + c]);
+        out[(long)t * W + c] = from_f32<T>(S * gelu_tanh_f(to_f32<T>(yraw[(long)t * ldy + c]) + yb));
+    }
+}
+
+// A decode step: one token per sequence, one thread per (sequence, channel).
+template <typename T>
+__global__ void diag_scan_decode_kernel(const float* __restrict__ a, const float* __restrict__ x, const T* __restrict__ yraw,
+                                        long ldy, const float* __restrict__ ybias, float* __restrict__ state, long state_stride,
+                                        T* __restrict__ out, const int* __restrict__ seq_slot, int n_seqs, int W) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_seqs * W) return;
+    const int b = (int)(idx / W), c = (int)(idx % W);
+    float* st = state + (long)seq_slot[b] * state_stride;
+    const float S = fmaf(a[idx], st[c], x[idx]);
+    st[c] = S;
+    out[idx] = from_f32<T>(S * gelu_tanh_f(to_f32<T>(yraw[(long)b * ldy + c]) + (ybias ? ybias[c] : 0.f)));
+}
+
+extern "C" int plm_diag_scan(const float* a, const float* x, const void* yraw, int dtype, long ldy, const float* ybias,
+                             float* state, long state_stride, void* out, const int* seq_start, const int* seq_slot, int n_seqs,
+                             int W, int is_decode, cudaStream_t stream) {
+    if (n_seqs <= 0) return PLM_OK;
+    if (W <= 0) return PLM_ERR_SHAPE;
+    if (dtype != PLM_F32 && dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    if (is_decode) {
+        const dim3 grid((unsigned)(((long)n_seqs * W + 255) / 256));
+        return plm_status_of(dtype == PLM_F32
+            ? launch_pdl(diag_scan_decode_kernel<float>, grid, dim3(256), 0, stream, a, x, (const float*)yraw, ldy, ybias, state,
+                         state_stride, (float*)out, seq_slot, n_seqs, W)
+            : launch_pdl(diag_scan_decode_kernel<bf16>, grid, dim3(256), 0, stream, a, x, (const bf16*)yraw, ldy, ybias, state,
+                         state_stride, (bf16*)out, seq_slot, n_seqs, W));
+    }
+    const dim3 grid((unsigned)((W + 31) / 32), (unsigned)n_seqs);
+    return plm_status_of(dtype == PLM_F32
+        ? launch_pdl(diag_scan_kernel<float>, grid, dim3(1024), 0, stream, a, x, (const float*)yraw, ldy, ybias, state, state_stride,
+                     (float*)out, seq_start, seq_slot, W)
+        : launch_pdl(diag_scan_kernel<bf16>, grid, dim3(1024), 0, stream, a, x, (const bf16*)yraw, ldy, ybias, state, state_stride,
+                     (bf16*)out, seq_start, seq_slot, W));
+}
+
+// ------------------------------------------------------------------------------------------------ gated delta rule
+// What the delta rule's recurrence takes, worked out per token in fp32 from the convolved projections:
+//   qn = q / sqrt(sum q^2 + l2_eps) * q_scale and kn = k / sqrt(sum k^2 + l2_eps) per key head, qk = qn . kn,
+//   dec[h, n] = exp(-exp(A_log[h]) * softplus(z[h, n] + dt_bias[h, n])),  beta[h] = sigmoid(braw[h]).
+// One block per token; a warp per key head, then per head.
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ z, long ldz,
+                  const T* __restrict__ braw, long ldb, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                  float l2_eps, float q_scale, float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ qk,
+                  float* __restrict__ dec, float* __restrict__ beta, int G, int H, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int job = warp; job < G + H; job += 4) {
+        if (job < G) {
+            const T* qr = q + (long)t * ldq + (long)job * N;
+            const T* kr = k + (long)t * ldk + (long)job * N;
+            float sq = 0.f, sk = 0.f, sqk = 0.f;
+            for (int i = lane; i < N; i += 32) {
+                const float a = to_f32<T>(qr[i]), b = to_f32<T>(kr[i]);
+                sq = fmaf(a, a, sq), sk = fmaf(b, b, sk), sqk = fmaf(a, b, sqk);
+            }
+            sq = warp_sum(sq), sk = warp_sum(sk), sqk = warp_sum(sqk);
+            const float rq = q_scale / sqrtf(sq + l2_eps), rk = 1.0f / sqrtf(sk + l2_eps);
+            float* qo = qn + ((long)t * G + job) * N;
+            float* ko = kn + ((long)t * G + job) * N;
+            for (int i = lane; i < N; i += 32) {
+                qo[i] = to_f32<T>(qr[i]) * rq;
+                ko[i] = to_f32<T>(kr[i]) * rk;
+            }
+            if (lane == 0) qk[(long)t * G + job] = sqk * rq * rk;
+        } else {
+            const int h = job - G;
+            const float rate = expf(a_log[h]);
+            const T* zr = z + (long)t * ldz + (long)h * N;
+            float* d = dec + ((long)t * H + h) * N;
+            for (int i = lane; i < N; i += 32) d[i] = expf(-rate * softplus_f(to_f32<T>(zr[i]) + dt_bias[(long)h * N + i]));
+            if (lane == 0) beta[(long)t * H + h] = sigmoid_f(to_f32<T>(braw[(long)t * ldb + h]));
+        }
+    }
+}
+
+extern "C" int plm_delta_prep(const void* q, long ldq, const void* k, long ldk, const void* z, long ldz, const void* braw, long ldb,
+                              int dtype, const float* a_log, const float* dt_bias, float l2_eps, float q_scale, float* qn, float* kn,
+                              float* qk, float* dec, float* beta, int n_tokens, int G, int H, int N, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (G <= 0 || H <= 0 || N <= 0) return PLM_ERR_SHAPE;
+    if (dtype == PLM_F32)
+        return plm_status_of(launch_pdl(delta_prep_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)q, ldq,
+                                        (const float*)k, ldk, (const float*)z, ldz, (const float*)braw, ldb, a_log, dt_bias, l2_eps,
+                                        q_scale, qn, kn, qk, dec, beta, G, H, N));
+    if (dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(delta_prep_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)q, ldq,
+                                        (const bf16*)k, ldk, (const bf16*)z, ldz, (const bf16*)braw, ldb, a_log, dt_bias, l2_eps,
+                                        q_scale, qn, kn, qk, dec, beta, G, H, N));
+    return PLM_ERR_DTYPE;
+}
+
+// The delta rule per head, token by token, state S [N, P] in fp32:
+//   S <- diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  (the read-out sees the write).
+// The columns of S do not meet, so a block takes 32 of them for one (sequence, head): a warp holds 8 columns, the N rows of
+// a column are dealt to 4 lanes (row n with lane n % 4), NR values of the state a thread.  Both sums over the rows,
+// k . (dec S) and q . (dec S), are taken in one pass before the write, and o = q . (dec S) + (q . k) u.
+#define DELTA_COLS 32
+template <typename T, int NR>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ qk,
+                  const float* __restrict__ dec, const float* __restrict__ beta, const T* __restrict__ v, long ldv,
+                  float* __restrict__ state, long state_stride, float* __restrict__ y, const int* __restrict__ seq_start,
+                  const int* __restrict__ seq_slot, int H, int N, int P, int heads_per_group, int TC) {
+    constexpr int NP = NR * 4;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                         // [TC][NP]
+    float* ks = qs + (long)TC * NP;
+    float* gs = ks + (long)TC * NP;
+    float* vs = gs + (long)TC * NP;           // [TC][DELTA_COLS]
+    float* bs = vs + (long)TC * DELTA_COLS;   // [TC] beta, then [TC] q . k
+    pdl_launch_dependents();
+    const int ptiles = (P + DELTA_COLS - 1) / DELTA_COLS;
+    int bid = blockIdx.x;
+    const int ptile = bid % ptiles;
+    bid /= ptiles;
+    const int h = bid % H, b = bid / H;
+    const int g = h / heads_per_group, G = H / heads_per_group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = (warp << 3) + (lane & 7), part = lane >> 3;
+    const int p = ptile * DELTA_COLS + col;
+    pdl_wait();
+    const int s0 = seq_start[b], s1 = seq_start[b + 1];
+    if (s1 <= s0) return;
+    float* st = state + (long)seq_slot[b] * state_stride + (long)h * N * P;
+    float S[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int n = r * 4 + part;
+        S[r] = (n < N && p < P) ? st[(long)n * P + p] : 0.f;
+    }
+    for (int base = s0; base < s1; base += TC) {
+        const int nt = min(TC, s1 - base);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * NP; idx += 128) {
+            const int tt = idx / NP, n = idx - tt * NP;
+            const long row = base + tt;
+            const bool in = n < N;
+            qs[idx] = in ? qn[(row * G + g) * N + n] : 0.f;
+            ks[idx] = in ? kn[(row * G + g) * N + n] : 0.f;
+            gs[idx] = in ? dec[(row * H + h) * N + n] : 1.f;
+        }
+        for (int idx = threadIdx.x; idx < nt * DELTA_COLS; idx += 128) {
+            const int tt = idx / DELTA_COLS, cc = idx - tt * DELTA_COLS;
+            const int pp = ptile * DELTA_COLS + cc;
+            vs[idx] = pp < P ? to_f32<T>(v[(long)(base + tt) * ldv + (long)h * P + pp]) : 0.f;
+        }
+        for (int tt = threadIdx.x; tt < nt; tt += 128) {
+            bs[tt] = beta[(long)(base + tt) * H + h];
+            bs[TC + tt] = qk[(long)(base + tt) * G + g];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* qt = qs + tt * NP + part;
+            const float* kt = ks + tt * NP + part;
+            const float* gt = gs + tt * NP + part;
+            float d1 = 0.f, d2 = 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const float s = S[r] * gt[r * 4];
+                S[r] = s;
+                d1 = fmaf(kt[r * 4], s, d1);
+                d2 = fmaf(qt[r * 4], s, d2);
+            }
+            d1 += __shfl_xor_sync(0xffffffffu, d1, 8);
+            d2 += __shfl_xor_sync(0xffffffffu, d2, 8);
+            d1 += __shfl_xor_sync(0xffffffffu, d1, 16);
+            d2 += __shfl_xor_sync(0xffffffffu, d2, 16);
+            const float u = bs[tt] * (vs[tt * DELTA_COLS + col] - d1);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) S[r] = fmaf(kt[r * 4], u, S[r]);
+            if (part == 0 && p < P) y[(long)(base + tt) * H * P + (long)h * P + p] = fmaf(bs[TC + tt], u, d2);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int n = r * 4 + part;
+        if (n < N && p < P) st[(long)n * P + p] = S[r];
+    }
+}
+
+template <typename T, int NR>
+static int delta_scan_launch(const float* qn, const float* kn, const float* qk, const float* dec, const float* beta, const void* v,
+                             long ldv, float* state, long state_stride, float* y, const int* seq_start, const int* seq_slot,
+                             int n_seqs, int H, int N, int P, int heads_per_group, cudaStream_t stream) {
+    const int TC = NR <= 32 ? 16 : 8;
+    const size_t smem = ((size_t)TC * NR * 4 * 3 + (size_t)TC * DELTA_COLS + 2 * TC) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_scan_kernel<T, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const unsigned grid = (unsigned)((long)n_seqs * H * ((P + DELTA_COLS - 1) / DELTA_COLS));
+    return plm_status_of(launch_pdl(delta_scan_kernel<T, NR>, dim3(grid), dim3(128), smem, stream, qn, kn, qk, dec, beta,
+                                    (const T*)v, ldv, state, state_stride, y, seq_start, seq_slot, H, N, P, heads_per_group, TC));
+}
+
+extern "C" int plm_delta_scan(const float* qn, const float* kn, const float* qk, const float* dec, const float* beta,
+                              const void* v, int dtype, long ldv, float* state, long state_stride, float* y, const int* seq_start,
+                              const int* seq_slot, int n_seqs, int H, int N, int P, int heads_per_group, cudaStream_t stream) {
+    if (n_seqs <= 0) return PLM_OK;
+    if (H <= 0 || N <= 0 || P <= 0 || heads_per_group <= 0 || H % heads_per_group) return PLM_ERR_SHAPE;
+    if (N > 256) return PLM_ERR_UNSUPPORTED;
+    if (dtype != PLM_F32 && dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    const int nr = (N + 3) / 4;
+#define DS(NR_)                                                                                                                 \
+    return dtype == PLM_F32                                                                                                     \
+               ? delta_scan_launch<float, NR_>(qn, kn, qk, dec, beta, v, ldv, state, state_stride, y, seq_start, seq_slot, n_seqs, \
+                                               H, N, P, heads_per_group, stream)                                               \
+               : delta_scan_launch<bf16, NR_>(qn, kn, qk, dec, beta, v, ldv, state, state_stride, y, seq_start, seq_slot, n_seqs, \
+                                              H, N, P, heads_per_group, stream)
+    if (nr <= 4) DS(4);
+    if (nr <= 8) DS(8);
+    if (nr <= 16) DS(16);
+    if (nr <= 24) DS(24);
+    if (nr <= 32) DS(32);
+    if (nr <= 48) DS(48);
+    DS(64);
+#undef DS
 }

@@ -25,6 +25,12 @@ def _join(*names: str) -> str:
     return ".".join(n for n in names if n)
 
 
+def _tensor_name(prefix: str, rel: str) -> str:
+    """The absolute name of a part's tensor: below the part's prefix, unless the part names a tensor of the whole
+    model by a leading "/"."""
+    return rel[1:] if rel.startswith("/") else _join(prefix, rel)
+
+
 class Model:
     def __init__(self, spec: ModelSpec, runtime: Optional[Runtime]):
         spec.validate()
@@ -34,6 +40,10 @@ class Model:
         self.blocks = [part_class("arrangement", layer.arrangement)(layer, runtime) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.lm_head, runtime)
+        # what runs of the schedule start with: one part that owns the table, and per run (entry, whether the
+        # embedding's output is added too)
+        self.run_input = build_part("run_input", spec.run_input, runtime) if spec.run_input is not None else None
+        self._run_inputs = {run: (index, bool(first)) for run, index, first in spec.run_input_at}
         self.loaded = False
         # Called as layer_hook(run, layer, done) before (done False) and after (done True) every scheduled layer
         # of a step: the reference's per-layer benchmark callback (bench_layer_cb_t, picolm/model.h:528-533,
@@ -50,6 +60,8 @@ class Model:
                 out.append((_join(layer.prefix, rel), part))
         out.append((self.spec.final_norm.prefix, self.final_norm))
         out.append((self.spec.lm_head.prefix, self.head))
+        if self.run_input is not None:
+            out.append((self.spec.run_input.prefix, self.run_input))
         return out
 
     def expected_tensors(self) -> Dict[str, WeightSpec]:
@@ -58,7 +70,7 @@ class Model:
         out: Dict[str, WeightSpec] = {}
         for prefix, part in self.named_parts():
             for rel, ws in part.weight_specs().items():
-                name = _join(prefix, rel)
+                name = _tensor_name(prefix, rel)
                 if name in out and out[name].shape != ws.shape:
                     raise ValueError(f"tensor {name!r} is wanted with shapes {out[name].shape} and {ws.shape}")
                 out.setdefault(name, ws)
@@ -68,7 +80,7 @@ class Model:
         """Hand every part its tensors; `get(name)` returns the device tensor
         (the same object for the same name, so tied weights stay one buffer)."""
         for prefix, part in self.named_parts():
-            part.load({rel: get(_join(prefix, rel)) for rel in part.weight_specs()})
+            part.load({rel: get(_tensor_name(prefix, rel)) for rel in part.weight_specs()})
         self.loaded = True
 
     def weight_bytes_per_step(self, tokens: int = 1) -> int:
@@ -139,7 +151,12 @@ class Model:
         stream = ResidualStream(self.embedding.forward(step))
         hook = self.layer_hook
         last = len(self.spec.schedule) - 1
+        # a later run may add the embedding's output once more: the layers change the stream in place, so keep a copy
+        first = stream.x.clone() if any(f for _, f in self._run_inputs.values()) else None
         for run, i in enumerate(self.spec.schedule):
+            if run in self._run_inputs:
+                index, add_first = self._run_inputs[run]
+                self.run_input.forward(stream, index, first if add_first else None)
             if hook is not None:
                 hook(run, i, False)
             block = self.blocks[i]

@@ -24,7 +24,11 @@ _SIGNATURES = {
     "plm_layernorm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_add_bias": [_vp, _vp, _i, _i, _vp],
     "plm_qk_norm_rope_store": [_vp, _i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                               _i, _i, _i, _i, _vp],
+                               _i, _i, _i, _i, _i, _i, _vp],
+    "plm_dyt_norm": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp],
+    "plm_add_rows": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+    "plm_scaled_sum": [_vp, _f, _vp, _vp, _f, _vp, _i, _i, _vp],
+    "plm_token_gate": [_vp, _i, _vp, _i, _l, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
     "plm_route_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
     "plm_moe_max_tiles": [_i, _i, _i],
     "plm_gate_constants": [_f, _f],
@@ -51,16 +55,20 @@ _SIGNATURES = {
     "plm_gemm_tc_wide_splits": [_i, _i, _i],
     "plm_gemm_tc_pair": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _l, _l, _l, _vp],
-    "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
-    "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
+    "plm_attention_rows": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "plm_attn_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "plm_attn_tc_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp],
+    "plm_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp],
     "plm_attn_decode_rope": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
     "plm_check_bounds": [_i, _i, _i, _i, _vp, _vp],
     "plm_decode_chain": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "plm_decode_chain_ctas": [],
     "plm_decode_chain_scratch": [_i, _i, _i],
-    "plm_causal_conv": [_vp, _i, _l, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "plm_causal_conv": [_vp, _i, _l, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
+    "plm_rglru_gates": [_vp, _i, _l, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "plm_diag_scan": [_vp, _vp, _vp, _i, _l, _vp, _vp, _l, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "plm_delta_prep": [_vp, _l, _vp, _l, _vp, _l, _vp, _l, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "plm_delta_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _l, _vp, _l, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_linear_scan": [_vp, _vp, _vp, _vp, _i, _l, _l, _l, _l, _i, _vp, _vp, _vp, _f, _f, _vp, _l, _vp, _l, _vp, _vp,
                         _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "plm_sigmoid_decay": [_vp, _i, _l, _vp, _f, _vp, _i, _i, _vp],

@@ -13,9 +13,13 @@ from ._lib import (PAGE_TOKENS, SM_COUNT, KernelError, _check, _dev, _dt, _fn, _
 
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                    tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
-                   window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   window: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of q [T, H, hd] over the paged cache; returns [T, H*hd].  `window` here and in the other kernels' faces:
-    a sliding window of that many keys, or the negative of a chunk size for a mask of chunks (`key_mask`)."""
+    a sliding window of that many keys, or the negative of a chunk size for a mask of chunks (`key_mask`).  `sink` here
+    and in the other faces: float32 [H], one more term exp(sink[h]) in the denominator of head h's softmax, with no key
+    and no value and outside the scale (None: the plain softmax)."""
+    _sink_check(sink, q.shape[1])
     _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
     T, H, hd = q.shape
@@ -29,8 +33,14 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     _cache_bounds("attention_simt", (), k_cache, block_table)
     _check(_fn("attention_simt", "plm_attention_rows")(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _dt(q, "q"), _p(tok_pos), _p(tok_seq), _p(block_table),
-        block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _stream()), f"attention_rows T={T} H={H} hd={hd}")
+        block_table.shape[1], T, H, G, hd, float(scale), int(window or 0), _p(sink), _stream()),
+        f"attention_rows T={T} H={H} hd={hd}")
     return out
+
+
+def _sink_check(sink: Optional[torch.Tensor], heads: int) -> None:
+    if sink is not None and (not sink.is_cuda or sink.dtype != torch.float32 or sink.shape != (heads,) or not sink.is_contiguous()):
+        raise KernelError(f"attention: the sink must be float32 [{heads}] on the device")
 
 
 def _cache_bounds(library, flags, k_cache, block_table) -> None:
@@ -60,10 +70,12 @@ def _attn_check(q, k_cache, v_cache, num_kv_heads):
 
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
                       seq_kv_len: torch.Tensor, block_table: torch.Tensor, max_new: int, num_kv_heads: int,
-                      scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                      sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q [T, H, hd])
     over its keys 0..seq_kv_len[b]-1 in the paged cache; returns [T, H*hd]."""
     T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
+    _sink_check(sink, H)
     _i32(seq_start, "seq_start"), _i32(seq_kv_len, "seq_kv_len"), _i32(block_table, "block_table")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
@@ -72,7 +84,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     _check(_fn(lib, "plm_attn_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale), int(window or 0),
-        _stream()), f"attention_prefill(mma) T={T} H={H} hd={hd}", flops=2 * H * hd * T * int(max_new))
+        _p(sink), _stream()), f"attention_prefill(mma) T={T} H={H} hd={hd}", flops=2 * H * hd * T * int(max_new))
     return out
 
 
@@ -84,12 +96,13 @@ def attention_tc_supported(q: torch.Tensor) -> bool:
 def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
                          seq_kv_len: torch.Tensor, block_table: torch.Tensor, max_new: int, num_kv_heads: int,
                          scale: float, window: Optional[int] = None,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`attention_prefill` on the tcgen05 tensor cores (scores and the page's output in tensor memory,
     operands by TMA): same arguments, same result up to rounding; head sizes 64 and 128."""
     T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
     if not attention_tc_supported(q):
         raise KernelError(f"attention_prefill_tc: head_dim {hd} of {q.dtype} is not supported (bfloat16, 64 or 128)")
+    _sink_check(sink, H)
     _i32(seq_start, "seq_start"), _i32(seq_kv_len, "seq_kv_len"), _i32(block_table, "block_table")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
@@ -98,7 +111,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _check(_fn(lib, "plm_attn_tc_prefill", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(seq_start), _p(seq_kv_len), _p(block_table),
         block_table.shape[1], k_cache.shape[0], T, seq_kv_len.numel(), int(max_new), H, num_kv_heads, float(scale),
-        int(window or 0), _p(status_word(q.device)), _stream()), f"attention_prefill_tc T={T} H={H} hd={hd}",
+        int(window or 0), _p(status_word(q.device)), _p(sink), _stream()), f"attention_prefill_tc T={T} H={H} hd={hd}",
         flops=2 * H * hd * T * int(max_new))
     return out
 
@@ -145,7 +158,7 @@ def decode_splits(n_tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                      tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
                      n_splits: int, window: Optional[int] = None, out: Optional[torch.Tensor] = None,
-                     scratch: Optional[bool] = None) -> torch.Tensor:
+                     scratch: Optional[bool] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of single query tokens (one per row of q [T, H, hd], at position tok_pos[t] of sequence
     tok_seq[t]) over the paged cache, the keys of each cut into `n_splits` ranges.  Up to eight ranges are the
     CTAs of a thread-block cluster and merge through its shared memory; more ranges, or more CTAs than
@@ -153,6 +166,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     one way or the other).  Returns [T, H*hd]."""
     T, H, hd = _attn_check(q, k_cache, v_cache, num_kv_heads)
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
+    _sink_check(sink, H)
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
     # Clusters are scheduled as a whole: past one wave of CTAs that costs more than the second kernel saves.
@@ -166,7 +180,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _check(_fn(lib, "plm_attn_decode", flags)(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(ws), _p(tok_pos), _p(tok_seq), _p(block_table),
         block_table.shape[1], T, H, num_kv_heads, float(scale), int(window or 0), int(n_splits), k_cache.shape[0],
-        _p(status_word(q.device)), _stream()),
+        _p(status_word(q.device)), _p(sink), _stream()),
         f"attention_decode T={T} H={H} hd={hd} splits={n_splits}", kernels=2 if scratch else 1)
     return out
 
@@ -239,19 +253,20 @@ def key_mask(window: Optional[int], chunk: Optional[int] = None) -> int:
     return -int(chunk) if chunk else int(window or 0)
 
 
-def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float, chunk: Optional[int] = None) -> torch.Tensor:
+def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float, chunk: Optional[int] = None,
+              sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the step's queries over their sequences' cached keys
     and values (`kv` is a `KVLayerCache`).  `chunk`: a mask of chunks of that many positions instead of the
-    cache's sliding window (see `key_mask`)."""
+    cache's sliding window (see `key_mask`).  `sink`: see `attention_rows`."""
     if chunk:
         kv = _MaskedView(kv, key_mask(kv.window, chunk))
     if attention_mma_supported(q):
         if step.is_decode:
             splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1, q.shape[2])
             return attention_decode(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
-                                    splits, window=kv.window)
+                                    splits, window=kv.window, sink=sink)
         prefill = attention_prefill_tc if attention_tc_supported(q) else attention_prefill
         return prefill(q, kv.k, kv.v, step.seq_start, step.seq_kv_len, kv.block_table, step.max_new,
-                       num_kv_heads, scale, window=kv.window)
+                       num_kv_heads, scale, window=kv.window, sink=sink)
     return attention_rows(q, kv.k, kv.v, step.tok_pos, step.tok_seq, kv.block_table, num_kv_heads, scale,
-                          window=kv.window)
+                          window=kv.window, sink=sink)

@@ -205,20 +205,25 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 
 def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
                        k_norm: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, kv, rotation, step,
-                       num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, own_kv: bool = True) -> None:
+                       num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, own_kv: bool = True,
+                       per_head: bool = False, values_from_keys: bool = False) -> None:
     """What stands between a QKV product and attention where queries and keys are normalised over all their heads at
     once: per token, in fp32, `q + bias` and `k + bias` are divided by their root mean square over ALL their columns
     and multiplied by `q_norm` / `k_norm` (None: no norm), the leading `rotation.rotary_dim` components of every head
     are rotated by the token's position, `v + bias` passes.  `qkv` [T, H*D (+ G*D + G*Dv)] float32 or the run's type;
     queries go to `q_out` [T, H, hd_c], keys and values (`own_kv`) into the pages of `kv` (a `KVLayerCache` whose
     head size hd_c >= D, Dv: what lies beyond a head's own width is written as zero).  `rotation`: `ops.Rotation` or
-    None."""
+    None.  `per_head`: the root mean square is taken over each head's own D columns, and `q_norm` / `k_norm` are [D],
+    serving every head.  `values_from_keys`: qkv holds no values; `k + bias` as projected, before norm and rotation,
+    is written as the value (Dv = D)."""
     _dev(qkv, "qkv"), _dev(q_out, "q_out")
     _i32(step.tok_pos, "tok_pos"), _i32(step.tok_seq, "tok_seq"), _i32(kv.block_table, "block_table")
     T = qkv.shape[0]
     H, G, D, Dv = num_heads, num_kv_heads, key_dim, value_dim
     hd_c = q_out.shape[2]
-    cols = H * D + ((G * D + G * Dv) if own_kv else 0)
+    if values_from_keys and (Dv != D or not own_kv):
+        raise KernelError("qk_norm_rope_store: keys that serve as values need value_dim == key_dim and keys of the layer's own")
+    cols = H * D + ((G * D + (0 if values_from_keys else G * Dv)) if own_kv else 0)
     if qkv.shape != (T, cols) or q_out.shape != (T, H, hd_c):
         raise KernelError("qk_norm_rope_store: qkv / q_out shapes do not match the head counts")
     if own_kv:
@@ -228,7 +233,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
                 raise KernelError(f"qk_norm_rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd_c}] of {q_out.dtype}")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape != (cols,) or not bias.is_cuda):
         raise KernelError("qk_norm_rope_store: bias must be float32, one per column of qkv")
-    for wn, n, size in ((q_norm, "q_norm", H * D), (k_norm if own_kv else None, "k_norm", G * D)):
+    for wn, n, size in ((q_norm, "q_norm", D if per_head else H * D), (k_norm if own_kv else None, "k_norm", D if per_head else G * D)):
         if wn is not None and (wn.dtype != q_out.dtype or wn.shape != (size,) or not wn.is_cuda):
             raise KernelError(f"qk_norm_rope_store: {n} must be [{size}] of {q_out.dtype}")
     cos = sin = None
@@ -245,5 +250,111 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
         _p(qkv), _dt(qkv, "qkv"), _p(bias), _p(q_norm), _p(k_norm) if own_kv else None, float(eps), _p(q_out),
         _p(kv.k) if own_kv else None, _p(kv.v) if own_kv else None, _dt(q_out, "q_out"), _p(cos), _p(sin),
         _p(step.tok_pos), _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, D, Dv, hd_c, rot,
-        0 if pairing == "half" else 1, 1 if own_kv else 0, _stream()), f"qk_norm_rope_store T={T}",
+        0 if pairing == "half" else 1, 1 if own_kv else 0, 1 if per_head else 0, 1 if values_from_keys else 0, _stream()),
+        f"qk_norm_rope_store T={T}",
         nbytes=qkv.numel() * qkv.element_size() + T * (H + (2 * G if own_kv else 0)) * hd_c * q_out.element_size())
+
+
+def _f32_vec(t: Optional[torch.Tensor], name: str, d: int) -> None:
+    if t is not None and (not t.is_cuda or t.dtype != torch.float32 or t.shape != (d,) or not t.is_contiguous()):
+        raise KernelError(f"{name} must be float32 [{d}] on the device")
+
+
+def dyt_norm(x: torch.Tensor, out_dtype: Optional[torch.dtype], alpha: Optional[torch.Tensor] = None,
+             weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, delta=None,
+             delta_bias: Optional[torch.Tensor] = None, post_weight: Optional[torch.Tensor] = None, post_eps: float = 0.0,
+             extra: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The norm without statistics on the fp32 stream `x` [T, d]: `tanh(alpha v) * weight + bias` elementwise, with
+    `v = x + delta' + delta_bias + extra`.  `delta` (fp32 [T, d], or a product that has not run) enters as it is, or,
+    with `post_weight` (fp32 [d]), divided by its own root mean square (`post_eps` inside the root) and multiplied
+    by post_weight; `delta_bias` is a vector [d], `extra` more rows [T, d], all float32.  v is written back to x
+    unless `rows` (int32) gathers.  alpha [1], weight, bias [d] float32.  Without `alpha` the result is v itself in
+    `out_dtype`; with `out_dtype` None nothing but the sum is made (returns None)."""
+    _dev(x, "x")
+    if x.dtype != torch.float32:
+        raise KernelError("the residual stream must be float32")
+    T, d = x.shape
+    if hasattr(delta, "compute"):
+        if rows is None and post_weight is None and delta.adds_in_place(x):
+            delta.add_into(x)
+            delta = None
+        else:
+            delta = delta.compute()
+    for t, n in ((delta, "delta"), (extra, "extra")):
+        if t is not None:
+            _dev(t, n)
+            if t.dtype != torch.float32 or t.shape != x.shape:
+                raise KernelError(f"{n} must be float32 and shaped like x")
+    _f32_vec(delta_bias, "delta_bias", d), _f32_vec(post_weight, "post_weight", d)
+    if alpha is not None:
+        _f32_vec(weight, "weight", d), _f32_vec(bias, "bias", d)
+        if weight is None or bias is None or not alpha.is_cuda or alpha.dtype != torch.float32 or alpha.numel() != 1:
+            raise KernelError("dyt_norm: alpha must be one float32 on the device, with a weight and a bias")
+    if post_weight is not None and delta is None:
+        raise KernelError("dyt_norm: post_weight without a delta")
+    n_rows = T
+    if rows is not None:
+        _i32(rows, "rows")
+        n_rows = rows.numel()
+    out = None if out_dtype is None else torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
+    if out is None and (rows is not None or (delta is None and delta_bias is None and extra is None)):
+        return None
+    set_bounds("elementwise", n_rows=T, device=x.device)
+    n_in = 1 + sum(t is not None for t in (delta, extra))
+    _check(_fn("elementwise", "plm_dyt_norm")(
+        _p(x), _p(delta), _p(delta_bias), _p(post_weight), float(post_eps), _p(extra), _p(alpha), _p(weight), _p(bias),
+        _p(out), _dt(out, "out") if out is not None else 0, _p(rows), n_rows, d, _stream()), f"dyt_norm rows={n_rows} d={d}",
+        nbytes=n_rows * d * (4 * n_in + (4 if n_in > 1 and rows is None else 0) + (out.element_size() if out is not None else 0)))
+    return out
+
+
+def add_rows(x: torch.Tensor, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None,
+             vec: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, d] += a + b + vec in place (float32; a, b rows like x, vec [d]; each may be None); returns x."""
+    _dev(x, "x")
+    if x.dtype != torch.float32 or x.dim() != 2:
+        raise KernelError("add_rows takes float32 rows [T, d]")
+    for t, n in ((a, "a"), (b, "b")):
+        if t is not None:
+            _dev(t, n)
+            if t.dtype != torch.float32 or t.shape != x.shape:
+                raise KernelError(f"add_rows: {n} must be float32 and shaped like x")
+    _f32_vec(vec, "vec", x.shape[1])
+    _check(_fn("elementwise", "plm_add_rows")(_p(x), _p(a), _p(b), _p(vec), x.shape[0], x.shape[1], _stream()), "add_rows",
+           nbytes=x.numel() * 4 * (2 + (a is not None) + (b is not None)))
+    return x
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float,
+               bias_a: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """scale_a * (a + bias_a) + scale_b * b for float32 rows a, b [T, d] and an optional float32 vector bias_a [d]."""
+    _dev(a, "a"), _dev(b, "b")
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.dim() != 2 or a.shape != b.shape:
+        raise KernelError("scaled_sum takes two float32 matrices of one shape")
+    _f32_vec(bias_a, "bias_a", a.shape[1])
+    out = torch.empty_like(a)
+    _check(_fn("elementwise", "plm_scaled_sum")(_p(a), float(scale_a), _p(bias_a), _p(b), float(scale_b), _p(out), a.shape[0],
+                                                a.shape[1], _stream()), "scaled_sum", nbytes=3 * a.numel() * 4)
+    return out
+
+
+def token_gate(gate: torch.Tensor, table: torch.Tensor, first_column: int, tokens: torch.Tensor,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r, j] = gelu_tanh(gate[r, j]) * table[tokens[row r], first_column + j] for `gate` [R, dim] and a per-token
+    `table` [vocab, columns] of gate's type; row r of gate belongs to token `rows[r]` of the step (None: token r)."""
+    _dev(gate, "gate"), _dev(table, "table"), _i32(tokens, "tokens")
+    R, dim = gate.shape
+    if table.dim() != 2 or table.dtype != gate.dtype or first_column < 0 or first_column + dim > table.shape[1]:
+        raise KernelError("token_gate: the table must be [vocab, columns] of the gate's type and hold the columns asked for")
+    if rows is not None:
+        _i32(rows, "rows")
+        if rows.numel() != R:
+            raise KernelError("token_gate: one row number per row of the gate")
+    elif tokens.numel() < R:
+        raise KernelError("token_gate: fewer tokens than rows")
+    out = torch.empty_like(gate)
+    set_bounds("elementwise", n_rows=tokens.numel(), device=gate.device)
+    _check(_fn("elementwise", "plm_token_gate")(
+        _p(gate), _dt(gate, "gate"), _p(table), _dt(table, "table"), table.shape[1], int(first_column), _p(tokens), _p(rows),
+        _p(out), R, dim, table.shape[0], _stream()), f"token_gate rows={R} dim={dim}", nbytes=3 * R * dim * gate.element_size())
+    return out

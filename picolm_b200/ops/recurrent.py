@@ -29,8 +29,10 @@ def _f32(t: Optional[torch.Tensor], name: str, numel: int) -> None:
         raise KernelError(f"{name} must be float32 with {numel} elements")
 
 
-def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step) -> torch.Tensor:
-    """Depthwise causal convolution over each sequence's tokens followed by SiLU.  `u` [T, C] (a column slice
+def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step,
+                in_bias: Optional[torch.Tensor] = None, activation: Optional[str] = "silu") -> torch.Tensor:
+    """Depthwise causal convolution over each sequence's tokens followed by SiLU (`activation=None`: by nothing);
+    `in_bias` [C] float32 is added to the step's inputs before they are used (and kept).  `u` [T, C] (a column slice
     will do), `weight` [taps, C] float32 (tap-major: a checkpoint's [C, taps] transposed) with the current token's
     tap last, `bias` [C] float32 or None, `state`
     float32 [slots, >= (taps - 1) * C] with contiguous rows: the last taps - 1 inputs of every sequence, oldest
@@ -40,7 +42,9 @@ def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     taps = weight.shape[0]
     if weight.dim() != 2 or weight.shape[1] != C:
         raise KernelError(f"causal_conv: the weights must be [taps, {C}], got {tuple(weight.shape)}")
-    _f32(weight, "weight", C * taps), _f32(bias, "bias", C)
+    _f32(weight, "weight", C * taps), _f32(bias, "bias", C), _f32(in_bias, "in_bias", C)
+    if activation not in ("silu", None):
+        raise KernelError(f"causal_conv: activation {activation!r} is not known (silu, None)")
     lds = _cols(state, "state")
     if state.dtype != torch.float32 or state.shape[1] < (taps - 1) * C:
         raise KernelError("causal_conv: the state must be float32 with (taps - 1) * C values a row")
@@ -49,7 +53,8 @@ def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     set_bounds("recurrent", n_seqs=step.n_seqs, device=u.device)
     _check(_fn("recurrent", "plm_causal_conv")(
         _p(u), _dt(u, "u"), ldu, _p(weight), _p(bias), _p(state), lds, _p(step.tok_seq), _p(step.seq_start),
-        _p(step.seq_slot), _p(out), T, step.n_seqs, C, taps, 1 if decode else 0, _stream()),
+        _p(step.seq_slot), _p(out), T, step.n_seqs, C, taps, 1 if decode else 0, _p(in_bias), 0 if activation == "silu" else 1,
+        _stream()),
         f"causal_conv T={T} C={C} taps={taps}", kernels=1 if decode or taps == 1 else 2,
         nbytes=2 * T * C * u.element_size())
     return out
@@ -210,3 +215,121 @@ def store_rows_paged(rows: torch.Tensor, pages: torch.Tensor, step, block_table:
     _check(_fn("recurrent", "plm_store_rows_paged")(
         _p(rows), _dt(rows, "rows"), ld, _p(pages), _p(step.tok_pos), _p(step.tok_seq), _p(block_table),
         block_table.shape[1], T, R, _stream()), f"store_rows_paged T={T} R={R}", nbytes=2 * T * R * rows.element_size())
+
+
+def rglru_gates(u: torch.Tensor, w_rate: torch.Tensor, w_in: torch.Tensor, b_rate: torch.Tensor, b_in: torch.Tensor,
+                rate: torch.Tensor, blocks: int):
+    """The two gates of a real-gated diagonal recurrence from its convolved input `u` [T, W] (a column slice will
+    do): the channels come in `blocks` equal parts, each with square matrices `w_rate[b]`, `w_in[b]` ([blocks, n, n],
+    [out, in], of u's type) and biases [W] float32;
+      a = exp(-sigmoid(w_rate[b] u_b + b_rate) * rate),   x = sqrt(1 - a^2) * sigmoid(w_in[b] u_b + b_in) * u
+    with `rate` [W] float32 (the constant times softplus of the learned parameter).  Sums and everything behind
+    them in float32; returns (a, x), float32 [T, W] each."""
+    ldu = _cols(u, "u")
+    T, W = u.shape
+    if blocks <= 0 or W % blocks:
+        raise KernelError(f"rglru_gates: {W} channels do not come in {blocks} equal blocks")
+    n = W // blocks
+    for w, name in ((w_rate, "w_rate"), (w_in, "w_in")):
+        _dev(w, name)
+        if tuple(w.shape) != (blocks, n, n) or w.dtype != u.dtype:
+            raise KernelError(f"rglru_gates: {name} must be [{blocks}, {n}, {n}] of {u.dtype}")
+    _f32(b_rate, "b_rate", W), _f32(b_in, "b_in", W), _f32(rate, "rate", W)
+    a = torch.empty((T, W), dtype=torch.float32, device=u.device)
+    x = torch.empty((T, W), dtype=torch.float32, device=u.device)
+    _check(_fn("recurrent", "plm_rglru_gates")(
+        _p(u), _dt(u, "u"), ldu, _p(w_rate), _p(w_in), _dt(w_rate, "w_rate"), _p(b_rate), _p(b_in), _p(rate), _p(a), _p(x),
+        T, W, blocks, _stream()), f"rglru_gates T={T} W={W} blocks={blocks}",
+        nbytes=T * W * (u.element_size() + 8) + 2 * W * n * w_rate.element_size(), flops=4 * T * W * n)
+    return a, x
+
+
+def diag_scan(a: torch.Tensor, x: torch.Tensor, y_raw: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
+              step) -> torch.Tensor:
+    """S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens (float32 `a`, `x` [T, W], contiguous), from
+    and into `state` (float32 [slots, >= W], contiguous rows); returns S_t * gelu_tanh(y_raw_t + y_bias) as [T, W] of
+    y_raw's type (`y_raw` may be a column slice; `y_bias` [W] float32 or None)."""
+    T, W = a.shape
+    for t, n in ((a, "a"), (x, "x")):
+        _dev(t, n)
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, W):
+            raise KernelError(f"diag_scan: {n} must be float32 [{T}, {W}]")
+    ldy = _cols(y_raw, "y_raw")
+    if tuple(y_raw.shape) != (T, W):
+        raise KernelError("diag_scan: y_raw must be shaped like a")
+    _f32(y_bias, "y_bias", W)
+    lds = _cols(state, "state")
+    if state.dtype != torch.float32 or state.shape[1] < W:
+        raise KernelError("diag_scan: the state must be float32 with a value per channel")
+    decode = bool(step.is_decode and step.n_tokens == step.n_seqs)
+    out = torch.empty((T, W), dtype=y_raw.dtype, device=a.device)
+    set_bounds("recurrent", n_seqs=step.n_seqs, device=a.device)
+    _check(_fn("recurrent", "plm_diag_scan")(
+        _p(a), _p(x), _p(y_raw), _dt(y_raw, "y_raw"), ldy, _p(y_bias), _p(state), lds, _p(out), _p(step.seq_start),
+        _p(step.seq_slot), step.n_seqs, W, 1 if decode else 0, _stream()), f"diag_scan T={T} W={W}",
+        nbytes=T * W * (8 * (1 if decode else 2) + 2 * y_raw.element_size()))
+    return out
+
+
+def delta_prep(q: torch.Tensor, k: torch.Tensor, z: torch.Tensor, b_raw: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, l2_eps: float, q_scale: float, heads: int, key_dim: int, heads_per_group: int = 1):
+    """What the gated delta rule's recurrence takes, per token in float32 from the convolved projections (all of one
+    type, column slices will do): q, k [T, groups * key_dim] made unit vectors per group (`x / sqrt(sum x^2 +
+    l2_eps)`, q also times `q_scale`), their product q . k, the decays `exp(-exp(a_log[h]) softplus(z + dt_bias))`
+    for z [T, heads * key_dim], and `sigmoid(b_raw)` for b_raw [T, heads].  Returns (qn, kn, qk, decay, beta)."""
+    T = q.shape[0]
+    H, N = heads, key_dim
+    if H % heads_per_group:
+        raise KernelError("delta_prep: heads is not a multiple of heads_per_group")
+    G = H // heads_per_group
+    ldq, ldk, ldz, ldb = _cols(q, "q"), _cols(k, "k"), _cols(z, "z"), _cols(b_raw, "b_raw")
+    if (tuple(q.shape) != (T, G * N) or tuple(k.shape) != (T, G * N) or tuple(z.shape) != (T, H * N)
+            or tuple(b_raw.shape) != (T, H) or not (q.dtype == k.dtype == z.dtype == b_raw.dtype)):
+        raise KernelError("delta_prep: q, k, z, b_raw do not have the shapes the head counts imply, or differ in type")
+    _f32(a_log, "a_log", H), _f32(dt_bias, "dt_bias", H * N)
+    dev = q.device
+    qn = torch.empty((T, G * N), dtype=torch.float32, device=dev)
+    kn = torch.empty((T, G * N), dtype=torch.float32, device=dev)
+    qk = torch.empty((T, G), dtype=torch.float32, device=dev)
+    dec = torch.empty((T, H * N), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, H), dtype=torch.float32, device=dev)
+    _check(_fn("recurrent", "plm_delta_prep")(
+        _p(q), ldq, _p(k), ldk, _p(z), ldz, _p(b_raw), ldb, _dt(q, "q"), _p(a_log), _p(dt_bias), float(l2_eps),
+        float(q_scale), _p(qn), _p(kn), _p(qk), _p(dec), _p(beta), T, G, H, N, _stream()), f"delta_prep T={T} H={H} N={N}",
+        nbytes=T * ((2 * G + H) * N * (q.element_size() + 4)))
+    return qn, kn, qk, dec, beta
+
+
+def delta_scan(qn: torch.Tensor, kn: torch.Tensor, qk: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor,
+               v: torch.Tensor, state: torch.Tensor, step, heads: int, key_dim: int, value_dim: int,
+               heads_per_group: int = 1) -> torch.Tensor:
+    """The gated delta rule over each sequence's tokens, per head, state S [key_dim, value_dim] in float32:
+      S <- diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+    (the read-out sees the token's own write).  qn, kn, qk, decay, beta as `delta_prep` returns them; v [T, heads *
+    value_dim] (a column slice will do); `state` float32 [slots, >= heads * key_dim * value_dim] with contiguous
+    rows holds S as [heads, key_dim, value_dim] and is carried on.  Returns o, float32 [T, heads * value_dim]."""
+    H, N, P = heads, key_dim, value_dim
+    T = v.shape[0]
+    if H % heads_per_group:
+        raise KernelError("delta_scan: heads is not a multiple of heads_per_group")
+    G = H // heads_per_group
+    ldv = _cols(v, "v")
+    for t, n, cols in ((qn, "qn", G * N), (kn, "kn", G * N), (qk, "qk", G), (decay, "decay", H * N), (beta, "beta", H)):
+        _dev(t, n)
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, cols):
+            raise KernelError(f"delta_scan: {n} must be float32 [{T}, {cols}]")
+    if tuple(v.shape) != (T, H * P):
+        raise KernelError("delta_scan: v must be [T, heads * value_dim]")
+    if N > 256:
+        raise KernelError(f"delta_scan: key_dim {N} exceeds 256, the largest state a thread's registers take")
+    lds = _cols(state, "state")
+    if state.dtype != torch.float32 or state.shape[1] < H * N * P:
+        raise KernelError("delta_scan: the state must be float32 with heads * key_dim * value_dim values a row")
+    y = torch.empty((T, H * P), dtype=torch.float32, device=v.device)
+    set_bounds("recurrent", n_seqs=step.n_seqs, device=v.device)
+    _check(_fn("recurrent", "plm_delta_scan")(
+        _p(qn), _p(kn), _p(qk), _p(decay), _p(beta), _p(v), _dt(v, "v"), ldv, _p(state), lds, _p(y), _p(step.seq_start),
+        _p(step.seq_slot), step.n_seqs, H, N, P, heads_per_group, _stream()), f"delta_scan T={T} H={H} N={N} P={P}",
+        nbytes=T * (2 * G * N + 2 * H * N) * 4 + T * H * P * (4 + v.element_size()) + 2 * step.n_seqs * H * N * P * 4,
+        flops=8 * T * H * N * P)
+    return y

@@ -19,6 +19,10 @@ Families and what `forward` takes and returns (T = tokens of the step):
                 norms, mixer and feed-forward are wired around the stream.
   embedding     forward(step) -> stream x [T, d] fp32.
   head          forward(h_rows) -> logits [rows, vocab] fp32.
+  token_input   forward(x, step, rows=None) -> delta fp32 from the stream's rows x (in the run's dtype) and the
+                tokens they belong to (`rows`: the step's row numbers of x's rows where the stream was narrowed).
+  run_input     forward(stream, index, first) adds what a run of the schedule starts with to the stream: entry
+                `index` of its own table and, with `first` (float32 rows), what the stream began as.
 """
 from __future__ import annotations
 
@@ -30,7 +34,7 @@ import torch
 from ..config.spec import PartSpec
 from ..runtime import Runtime
 
-FAMILIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "embedding", "head")
+FAMILIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "embedding", "head", "token_input", "run_input")
 
 
 @dataclass(frozen=True)

@@ -20,7 +20,7 @@ from typing import List
 
 from ..config.spec import LayerSpec, PartSpec
 from .base import Part, build_part, register_part
-from .stream import PostNormed
+from .stream import PostNormed, settle
 
 
 class Arrangement(Part):
@@ -51,7 +51,18 @@ class Arrangement(Part):
                 if getattr(part, "cache_spec", None) is not None and part.cache_spec() is not None]
 
     def cache_specs(self):
-        return [self.named[name].cache_spec() for name in self.cache_owners()]
+        """One entry per thing kept; a part that keeps several (`cache_specs()` of its own) has them side by side."""
+        out = []
+        for name in self.cache_owners():
+            part = self.named[name]
+            out.extend(part.cache_specs() if hasattr(part, "cache_specs") else [part.cache_spec()])
+        return out
+
+    def _mixer_cache(self, caches):
+        """What the mixer is handed of the layer's caches: its one cache, or all of them if it keeps several."""
+        if hasattr(self.mixer, "cache_specs"):
+            return caches
+        return caches[0] if caches else None
 
     def prepare(self, max_seq_tokens: int) -> None:
         for part in self.named.values():
@@ -71,7 +82,7 @@ class Arrangement(Part):
 @register_part("arrangement", "pre_norm")
 class PreNormBlock(Arrangement):
     """`x += mixer(norm(x)); x += feed_forward(norm'(x))`; the feed-forward and its norm are optional (a layer that
-    only mixes)."""
+    only mixes).  Optional too: `token_input` with `token_input_norm`, a last step `x += norm''(input(x, token))`."""
     wants = ("mixer_norm", "mixer")
 
     narrows_rows = True
@@ -81,24 +92,33 @@ class PreNormBlock(Arrangement):
         has seen all tokens, the stream is narrowed to those rows and the feed-forward runs on them alone; with
         no row to keep, nothing runs after the mixer."""
         h = self._norm(self.mixer_norm, self.mixer, stream)
-        stream.pending = self.mixer.forward(h, step, caches[0] if caches else None)
+        stream.pending = self.mixer.forward(h, step, self._mixer_cache(caches))
         if keep_rows is not None:
             if keep_rows.numel() == 0:
                 stream.pending = None
                 return
             stream.narrow(keep_rows)
-        if "feed_forward" not in self.named:
-            return
-        h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
-        stream.pending = self.feed_forward.forward(h, step)
+        if "feed_forward" in self.named:
+            h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
+            stream.pending = self.feed_forward.forward(h, step)
+        if "token_input" in self.named:
+            # an input from the token itself, gated by the stream as the sublayers leave it; its result passes a norm
+            # of its own before it is added, which is left to whatever reads the stream next
+            x = settle(stream, self.runtime.dtype)
+            stream.pending = PostNormed(self.token_input.forward(x, step, rows=keep_rows), self.token_input_norm)
 
 
 def pre_norm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
-                   feed_forward_norm: PartSpec, cache_of=None) -> LayerSpec:
-    """The spec of a `pre_norm` layer from its four parts; without `feed_forward` the layer only mixes."""
+                   feed_forward_norm: PartSpec, cache_of=None, token_input: PartSpec = None,
+                   token_input_norm: PartSpec = None) -> LayerSpec:
+    """The spec of a `pre_norm` layer from its four parts; without `feed_forward` the layer only mixes.  With
+    `token_input` (family "token_input") and `token_input_norm` (an RMS norm) the layer ends with `x += norm(input(x,
+    token))`."""
     parts = {"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer)}
     if feed_forward is not None:
         parts.update({"feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward)})
+    if token_input is not None:
+        parts.update({"token_input": ("token_input", token_input), "token_input_norm": ("norm", token_input_norm)})
     return LayerSpec(prefix, "pre_norm", parts, cache_of=cache_of)
 
 
@@ -117,7 +137,7 @@ class SandwichNormBlock(Arrangement):
 
     def forward(self, stream, step, caches, keep_rows=None):
         h = self.mixer_norm.forward(stream)
-        delta = self._rows(self.mixer.forward(h, step, caches[0] if caches else None))
+        delta = self._rows(self.mixer.forward(h, step, self._mixer_cache(caches)))
         if keep_rows is not None:
             # the last layer of a step: only these rows are read afterwards, and the norms go row by row
             if keep_rows.numel() == 0:

@@ -44,7 +44,12 @@ class Attention(Part):
       bias          True: q, k, v and o have biases, tensors `<name><bias_suffix>` (default ".b")
       qk_norm       {"eps", "q_name", "k_name"}: queries and keys are divided by their root mean square over ALL heads
                     at once and multiplied by those weights ([H * head_dim], [G * head_dim]), after the bias and
-                    before the rotation
+                    before the rotation; with "per_head": True the root mean square is each head's own and the
+                    weights are [head_dim], shared by the heads
+      values_from_keys  True: there is no value projection; the keys as projected (bias added, before norm and
+                    rotation) serve as values
+      sink_name     a tensor [num_heads]: the softmax's denominator of head h also holds exp(sink[h]), a term with no
+                    key and no value that the scale does not touch
       own_kv        False: the layer has no key and value tensors (projections, biases, key norm); it attends over
                     what the layer it borrows its cache from wrote
     With any of value_dim, bias, qk_norm or own_kv=False, what stands between the QKV product and attention is one
@@ -76,9 +81,15 @@ class Attention(Part):
         self.vd = int(p.get("value_dim") or self.hd)
         self.bias = bool(p.get("bias", False))
         self.qk_norm = p.get("qk_norm")
+        self.per_head_norm = bool(self.qk_norm and self.qk_norm.get("per_head", False))
         self.own_kv = bool(p.get("own_kv", True))
+        self.v_from_k = bool(p.get("values_from_keys", False))
+        if self.v_from_k and (self.vd != self.hd or not self.own_kv):
+            raise ValueError("keys that serve as values need value_dim == head_dim and keys of the layer's own")
+        self.sink_name = p.get("sink_name")
         # the general form: its own kernel between the product and attention, a cache of padded heads
-        self.general = self.vd != self.hd or self.bias or self.qk_norm is not None or not self.own_kv
+        self.general = (self.vd != self.hd or self.bias or self.qk_norm is not None or not self.own_kv or self.v_from_k
+                        or self.sink_name is not None)
         self.hd_c = -(-max(self.hd, self.vd) // 16) * 16 if self.general else self.hd
         pos = p.get("position") or PartSpec("none")
         self.position = build_part("position", pos, runtime)
@@ -89,22 +100,25 @@ class Attention(Part):
     def _names(self):
         """(tensor names of the projections that feed attention, in the order of their rows in the one product)."""
         p = self.params
-        return [p["q_name"]] + ([p["k_name"], p["v_name"]] if self.own_kv else [])
+        return [p["q_name"]] + (([p["k_name"]] if self.v_from_k else [p["k_name"], p["v_name"]]) if self.own_kv else [])
 
     def weight_specs(self):
         p, H, G, hd, vd, d = self.params, self.H, self.G, self.hd, self.vd, self.d
         specs = {p["q_name"]: WeightSpec((H * hd, d)), p["o_name"]: WeightSpec((d, H * vd))}
         if self.own_kv:
             specs[p["k_name"]] = WeightSpec((G * hd, d))
-            specs[p["v_name"]] = WeightSpec((G * vd, d))
+            if not self.v_from_k:
+                specs[p["v_name"]] = WeightSpec((G * vd, d))
+        if self.sink_name is not None:
+            specs[self.sink_name] = WeightSpec((H,), init="normal_scaled", scale=1.0)
         if self.bias:
             sfx = p.get("bias_suffix", ".b")
             for name in self._names() + [p["o_name"]]:
                 specs[name + sfx] = WeightSpec((specs[name].shape[0],), init="normal")
         if self.qk_norm is not None:
-            specs[self.qk_norm["q_name"]] = WeightSpec((H * hd,), init="ones_normal")
+            specs[self.qk_norm["q_name"]] = WeightSpec((hd if self.per_head_norm else H * hd,), init="ones_normal")
             if self.own_kv:
-                specs[self.qk_norm["k_name"]] = WeightSpec((G * hd,), init="ones_normal")
+                specs[self.qk_norm["k_name"]] = WeightSpec((hd if self.per_head_norm else G * hd,), init="ones_normal")
         return specs
 
     def load(self, tensors):
@@ -113,6 +127,7 @@ class Attention(Part):
         self.w_qkv = _stack_rows([tensors[n] for n in self._names()])
         self.w_o = tensors[p["o_name"]]
         self.b_qkv = self.b_o = self.w_qn = self.w_kn = None
+        self.sink = None if self.sink_name is None else tensors[self.sink_name].to(torch.float32).contiguous()
         if self.bias:
             sfx = p.get("bias_suffix", ".b")
             self.b_qkv = torch.cat([tensors[n + sfx].to(torch.float32) for n in self._names()]).contiguous()
@@ -147,8 +162,9 @@ class Attention(Part):
         q = torch.empty((h.shape[0], self.H, self.hd_c), dtype=dt, device=h.device)
         rotation = self.position.rotation() if hasattr(self.position, "rotation") else None
         ops.qk_norm_rope_store(qkv, self.b_qkv, self.w_qn, self.w_kn, self.qk_norm["eps"] if self.qk_norm else 0.0, q,
-                               cache, rotation, step, self.H, self.G, self.hd, self.vd, own_kv=self.own_kv)
-        ctx = ops.attention(q, cache, step, self.G, self.scale, chunk=self.chunk)
+                               cache, rotation, step, self.H, self.G, self.hd, self.vd, own_kv=self.own_kv,
+                               per_head=self.per_head_norm, values_from_keys=self.v_from_k)
+        ctx = ops.attention(q, cache, step, self.G, self.scale, chunk=self.chunk, sink=self.sink)
         delta = ops.linear(ctx, self.w_o, torch.float32, defer=True)
         return BiasedDelta(delta, self.b_o) if self.b_o is not None else delta
 
@@ -168,3 +184,69 @@ class Attention(Part):
             self.position.apply(qkv, q, cache, step, self.H, self.G, self.hd)
             ctx = ops.attention(q, cache, step, self.G, self.scale, chunk=self.chunk)
         return ops.linear(ctx, self.w_o, torch.float32, defer=True)
+
+
+def _rows(delta):
+    """(float32 rows, bias vector or None) of a mixer's result, whatever form it was handed back in."""
+    bias = None
+    if isinstance(delta, BiasedDelta):
+        delta, bias = delta.delta, delta.bias
+    if hasattr(delta, "compute"):
+        delta = delta.compute()
+    return delta, bias
+
+
+@register_part("mixer", "parallel")
+class ParallelMixers(Part):
+    """Two mixers side by side that read the same normed rows; the result is `left_scale * left + right_scale *
+    right`.  params: left, right (`PartSpec`s of the mixer family; their `prefix` is where their tensors live below
+    this part's), left_scale, right_scale.  Each half keeps what it keeps in the cache: the layer's caches are the
+    left's, then the right's (`cache_specs`), and `forward` takes them as a list."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.halves = [(self.params[side].prefix, build_part("mixer", self.params[side], runtime)) for side in ("left", "right")]
+        self.scales = (float(self.params["left_scale"]), float(self.params["right_scale"]))
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(bool(getattr(part, "graph_safe", False)) for _, part in self.halves)
+
+    @property
+    def graph_safe_prompts(self) -> bool:
+        return all(bool(getattr(part, "graph_safe_prompts", False)) for _, part in self.halves)
+
+    def weight_specs(self):
+        return {(f"{prefix}.{name}" if prefix else name): ws for prefix, part in self.halves
+                for name, ws in part.weight_specs().items()}
+
+    def load(self, tensors):
+        for prefix, part in self.halves:
+            part.load({name: tensors[f"{prefix}.{name}" if prefix else name] for name in part.weight_specs()})
+
+    def weight_bytes(self):
+        return sum(part.weight_bytes() for _, part in self.halves)
+
+    def cache_specs(self):
+        return [s for _, part in self.halves for s in ([part.cache_spec()] if part.cache_spec() is not None else [])]
+
+    def cache_spec(self):
+        specs = self.cache_specs()
+        return specs[0] if specs else None
+
+    def prepare(self, max_seq_tokens: int) -> None:
+        for _, part in self.halves:
+            prep = getattr(part, "prepare", None)
+            if prep is not None:
+                prep(max_seq_tokens)
+
+    def forward(self, h, step, caches):
+        caches = list(caches)
+        results = []
+        for _, part in self.halves:
+            cache = caches.pop(0) if part.cache_spec() is not None else None
+            results.append(_rows(part.forward(h, step, cache)))
+        (left, left_bias), (right, right_bias) = results
+        if right_bias is not None:
+            right = ops.add_bias(right, right_bias)
+        return ops.scaled_sum(left, self.scales[0], right, self.scales[1], bias_a=left_bias)

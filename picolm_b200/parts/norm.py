@@ -10,7 +10,7 @@ import torch
 
 from .. import ops
 from .base import Part, WeightSpec, register_part
-from .stream import BiasedDelta, PostNormed, ResidualStream
+from .stream import BiasedDelta, PostNormed, ResidualStream, pending_addends
 
 
 @register_part("norm", "rmsnorm")
@@ -30,6 +30,13 @@ class RMSNorm(Part):
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
+
+    def weight_f32(self) -> torch.Tensor:
+        """The weight in float32 (made once), for kernels that apply this norm to a float32 delta on the way."""
+        w = getattr(self, "_weight_f32", None)
+        if w is None:
+            w = self._weight_f32 = self.weight.to(torch.float32).contiguous()
+        return w
 
     can_defer_scale = True
     graph_safe = True
@@ -102,6 +109,48 @@ class LayerNorm(Part):
         if isinstance(p, BiasedDelta):
             p, bias = p.delta, p.bias
         h = ops.layernorm(stream.x, self.weight, self.params["eps"], self.runtime.dtype, delta=p, bias=bias, rows=rows)
+        if rows is None:
+            stream.pending = None
+        return h
+
+
+@register_part("norm", "dyt")
+class DynamicTanh(Part):
+    """A norm that computes no mean and no variance: `tanh(alpha * x) * w + b` elementwise, alpha one learned number.
+    params: size, name (the weight's tensor name relative to the part's prefix, "" for the prefix alone; default
+    "weight"), alpha_name and bias_name (default: the weight's name with ".alpha" / ".b" added).  Tensors: weight and
+    bias [size], alpha [].  Everything in float32 on the float32 stream."""
+
+    graph_safe = True
+    graph_safe_prompts = True
+
+    def _names(self):
+        base = self.params.get("name", "weight")
+        sub = (lambda s: (base + "." + s) if base else s)
+        return base, self.params.get("alpha_name", sub("alpha")), self.params.get("bias_name", sub("b"))
+
+    def weight_specs(self):
+        w, a, b = self._names()
+        n = self.params["size"]
+        return {w: WeightSpec((n,), init="ones_normal"), a: WeightSpec((), init="uniform", lo=0.4, hi=1.2),
+                b: WeightSpec((n,), init="normal")}
+
+    def load(self, tensors):
+        w, a, b = self._names()
+        self.weight = tensors[w].to(torch.float32).contiguous()
+        self.alpha = tensors[a].to(torch.float32).reshape(1).contiguous()
+        self.bias = tensors[b].to(torch.float32).contiguous()
+
+    def weight_bytes(self):
+        return 4 * (self.weight.numel() + self.bias.numel() + 1)
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, defer_scale: bool = False):
+        """The norm of `x + pending`: a pending delta, its bias or its own RMS norm are added in the same pass.
+        Without `rows` the sum is written back to the stream and the delta is consumed; with `rows` only those rows
+        are normalised and the stream is left as it is."""
+        delta, bias, post_w, post_eps = pending_addends(stream.pending)
+        h = ops.dyt_norm(stream.x, self.runtime.dtype, alpha=self.alpha, weight=self.weight, bias=self.bias, delta=delta,
+                         delta_bias=bias, post_weight=post_w, post_eps=post_eps, rows=rows)
         if rows is None:
             stream.pending = None
         return h

@@ -13,7 +13,8 @@ RoPE as the reference builds and applies it: `theta(p, i) = p / base^(2i/rot)`,
 pairings: adjacent `(x[2i], x[2i+1])` for its permuted GGUF Llama files and
 half-split `(x[i], x[i+rot/2])` (picolm/tensor.c:3220-3235), which is how
 safetensors checkpoints are laid out.  The llama3 frequency scaling is not in the
-reference; it is the rule Llama-3 checkpoints state in `rope_scaling`.
+reference; it is the rule Llama-3 checkpoints state in `rope_scaling`.  Nor is YaRN
+(`rope_type: "yarn"` with `factor`, `original`, `fast`, `slow`), which also scales cos and sin.
 """
 from __future__ import annotations
 
@@ -34,6 +35,8 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[di
     if not scaling:
         return inv
     kind = scaling.get("rope_type")
+    if kind == "yarn":
+        return _yarn_frequencies(inv, rotary_dim, theta, scaling)
     if kind != "llama3":
         raise ValueError(f"rope scaling of type {kind!r} is not supported")
     factor, low, high = float(scaling["factor"]), float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
@@ -49,6 +52,32 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[di
             smooth = (L0 / wavelen - low) / (high - low)
             out.append((1.0 - smooth) * f / factor + smooth * f)
     return out
+
+
+def _yarn_frequencies(inv: List[float], rotary_dim: int, theta: float, scaling: dict) -> List[float]:
+    """YaRN: a pair whose wavelength fits `fast` times or more into the `original` context keeps its frequency, one
+    that fits `slow` times or less has it divided by `factor`, and the pairs between are blended along a ramp that is
+    linear in the pair's number.  With n(t) = rot * ln(original / (2 pi t)) / (2 ln theta), the pair that turns t times
+    in the original context, the ramp runs from lo = max(floor(n(fast)), 0) to hi = min(ceil(n(slow)), rot - 1)."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), rotary_dim - 1)
+    out = []
+    for i, f in enumerate(inv):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return out
+
+
+def rope_magnitude(scaling: Optional[dict]) -> float:
+    """What cos and sin are both multiplied by: 0.1 ln(factor) + 1 under YaRN, else 1."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 @register_part("position", "rope")
@@ -78,8 +107,9 @@ class RotaryEncoding(Part):
                                                     self.params.get("scaling")), dtype=torch.float64)
         pos = torch.arange(n_positions, dtype=torch.float64)
         ang = pos[:, None] * inv[None, :]
-        self.cos = ang.cos().to(torch.float32).to(self.runtime.device).contiguous()
-        self.sin = ang.sin().to(torch.float32).to(self.runtime.device).contiguous()
+        mag = rope_magnitude(self.params.get("scaling"))
+        self.cos = (ang.cos() * mag).to(torch.float32).to(self.runtime.device).contiguous()
+        self.sin = (ang.sin() * mag).to(torch.float32).to(self.runtime.device).contiguous()
 
     def rotation(self):
         """The encoding as data (`ops.Rotation`), for a kernel that applies it itself."""

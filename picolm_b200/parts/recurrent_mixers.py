@@ -149,3 +149,147 @@ class GatedLinearAttention(_StateMixer):
         gated = ops.gated_norm(o, dt, weight=self.norm_w, eps=self.eps, group=self.P, weight_per_group=True, gate=g,
                                gate_mode=ops.GATE_AFTER_NORM, activation="silu")
         return ops.linear(gated, self.w_o, torch.float32, defer=True)
+
+
+@register_part("mixer", "rglru")
+class GatedDiagonalRecurrence(_StateMixer):
+    """A recurrent block around a real-gated diagonal linear recurrence.  params: hidden_size, width (channels of the
+    recurrence), blocks (the gates' matrices are block-diagonal in that many equal parts), conv (taps), rate (the
+    constant c of the decay, default 8).  Two branches read h: `y = gelu_tanh(W_y h + b_y)` and
+    `u = conv(W_x h + b_x)` (depthwise, causal, with a bias and no activation).  Per block b of u:
+    `r = sigmoid(ra[b] u_b + ra.b)`, `i = sigmoid(ri[b] u_b + ri.b)`; `a = exp(-c r softplus(lam))`;
+    `S_t = a S_(t-1) + sqrt(1 - a^2) i u` from S = 0, the first token like every other; the result is `W_o (S y)`.
+
+    Tensors: y, x [width, hidden] with biases y.b, x.b; conv [width, taps], conv.b; ra, ri [blocks, n, n] ([out, in],
+    n = width / blocks) with ra.b, ri.b [blocks, n]; lam [width]; o [hidden, width]."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        p = self.params
+        self.d, self.W, self.blocks, self.taps = p["hidden_size"], p["width"], p["blocks"], p["conv"]
+        self.c = float(p.get("rate", 8.0))
+        if self.W % self.blocks:
+            raise ValueError("rglru: width must be a multiple of blocks")
+        self.n_conv = (self.taps - 1) * self.W
+
+    def weight_specs(self):
+        W, d, B = self.W, self.d, self.blocks
+        n = W // B
+        return {
+            "y": WeightSpec((W, d)), "y.b": WeightSpec((W,), init="normal"),
+            "x": WeightSpec((W, d)), "x.b": WeightSpec((W,), init="normal"),
+            "conv": WeightSpec((W, self.taps), init="normal_scaled", scale=0.4),
+            "conv.b": WeightSpec((W,), init="normal_scaled", scale=0.1),
+            "ra": WeightSpec((B, n, n)), "ra.b": WeightSpec((B, n), init="normal"),
+            "ri": WeightSpec((B, n, n)), "ri.b": WeightSpec((B, n), init="normal"),
+            "lam": WeightSpec((W,), init="uniform", lo=-4.0, hi=0.0),
+            "o": WeightSpec((d, W)),
+        }
+
+    def load(self, tensors):
+        self.w_yx = _stack_rows([tensors["y"], tensors["x"]])       # one product for both branches: rows [y | x]
+        self.w_o = tensors["o"]
+        self.y_bias, self.x_bias = self._f32(tensors["y.b"]), self._f32(tensors["x.b"])
+        self.conv_w, self.conv_b = self._f32(tensors["conv"].to(torch.float32).t()), self._f32(tensors["conv.b"])
+        self.w_ra, self.w_ri = tensors["ra"].contiguous(), tensors["ri"].contiguous()
+        self.b_ra, self.b_ri = self._f32(tensors["ra.b"]).reshape(-1), self._f32(tensors["ri.b"]).reshape(-1)
+        # the decay's exponent per channel, c * softplus(lam), once in float32
+        self.rate = (self.c * torch.nn.functional.softplus(tensors["lam"].to(torch.float32))).contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_yx, self.w_o, self.w_ra, self.w_ri))
+
+    def cache_spec(self):
+        # one row per sequence: the recurrence's state [width], then the convolution's last inputs
+        return CacheSpec.state((self.W + self.n_conv,))
+
+    def forward(self, h, step, cache):
+        dt, W = self.runtime.dtype, self.W
+        yx = ops.linear(h, self.w_yx, dt)
+        u = ops.causal_conv(yx[:, W:], self.conv_w, self.conv_b, cache.state[:, W:], step, in_bias=self.x_bias,
+                            activation=None)
+        a, x = ops.rglru_gates(u, self.w_ra, self.w_ri, self.b_ra, self.b_ri, self.rate, self.blocks)
+        g = ops.diag_scan(a, x, yx[:, :W], self.y_bias, cache.state[:, :W], step)
+        return ops.linear(g, self.w_o, torch.float32, defer=True)
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaRule(_StateMixer):
+    """The delta rule with a decay per key channel.  params: hidden_size, heads, kv_heads (query/key heads; head h
+    uses q/k head h // (heads / kv_heads)), dim (key size), vdim, conv (taps), rank (None: as the checkpoint's a1 and
+    g1 have it), eps (of the read-out's norm), l2_eps (inside the root of the unit norm, default 1e-6).
+    q, k, v each pass a depthwise causal convolution (no bias) and SiLU; q and k are made unit vectors per head and q
+    is multiplied by dim^(-1/2); `beta = sigmoid(W_b h)` per head; the decay per head and key channel is
+    `exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias))`.  Per head, S [dim, vdim] from zero:
+    `S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`.  Each head's o is divided by its root
+    mean square over vdim, times `norm` [vdim] (shared), times `sigmoid(W_g2 (W_g1 h))`, then projected.
+
+    Tensors: q, k [kv_heads dim, hidden], v [heads vdim, hidden], q.conv, k.conv, v.conv [channels, taps], b [heads,
+    hidden], A_log [heads], a1 [rank, hidden], a2 [heads dim, rank], dt_bias [heads dim], g1 [rank', hidden], g2
+    [heads vdim, rank'], norm [vdim], o [hidden, heads vdim]."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        p = self.params
+        self.d, self.H, self.G, self.N, self.P = p["hidden_size"], p["heads"], p["kv_heads"], p["dim"], p["vdim"]
+        self.taps, self.rank, self.eps = p["conv"], p.get("rank"), float(p["eps"])
+        self.l2_eps = float(p.get("l2_eps", 1e-6))
+        if self.H % self.G:
+            raise ValueError("gated_delta: heads must be a multiple of kv_heads")
+        self.conv_channels = 2 * self.G * self.N + self.H * self.P
+        self.n_state = self.H * self.N * self.P
+        self.n_conv = (self.taps - 1) * self.conv_channels
+
+    def weight_specs(self):
+        GN, HN, HP, d, r = self.G * self.N, self.H * self.N, self.H * self.P, self.d, self.rank or -1
+        conv = dict(init="normal_scaled", scale=0.4)
+        return {
+            "q": WeightSpec((GN, d)), "k": WeightSpec((GN, d)), "v": WeightSpec((HP, d)),
+            "q.conv": WeightSpec((GN, self.taps), **conv), "k.conv": WeightSpec((GN, self.taps), **conv),
+            "v.conv": WeightSpec((HP, self.taps), **conv),
+            "b": WeightSpec((self.H, d)), "A_log": WeightSpec((self.H,), init="uniform", lo=-2.0, hi=0.5),
+            "a1": WeightSpec((r, d)), "a2": WeightSpec((HN, r), init="normal_scaled", scale=0.5),
+            "dt_bias": WeightSpec((HN,), init="uniform", lo=-3.0, hi=0.0),
+            "g1": WeightSpec((r, d)), "g2": WeightSpec((HP, r), init="normal_scaled", scale=0.5),
+            "norm": WeightSpec((self.P,), init="ones_normal"),
+            "o": WeightSpec((d, HP)),
+        }
+
+    def load(self, tensors):
+        # one projection for everything that reads h: rows [q | k | v | b | a1 | g1]
+        self.w_h = _stack_rows([tensors[n] for n in ("q", "k", "v", "b", "a1", "g1")])
+        self.r_a, self.r_g = tensors["a1"].shape[0], tensors["g1"].shape[0]
+        self.w_a2, self.w_g2, self.w_o = tensors["a2"], tensors["g2"], tensors["o"]
+        if self.w_a2.shape[1] != self.r_a or self.w_g2.shape[1] != self.r_g:
+            raise ValueError("gated_delta: a2 / g2 do not take as many columns as a1 / g1 have rows")
+        self.conv_w = self._f32(torch.cat([tensors[n].to(torch.float32) for n in ("q.conv", "k.conv", "v.conv")]).t())
+        self.a_log, self.dt_bias = self._f32(tensors["A_log"]), self._f32(tensors["dt_bias"])
+        self.norm_w = self._f32(tensors["norm"])
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_h, self.w_a2, self.w_g2, self.w_o))
+
+    def cache_spec(self):
+        # one row per sequence: S as [heads, dim, vdim], then the convolution's last inputs
+        return CacheSpec.state((self.n_state + self.n_conv,))
+
+    def _narrow_product(self, cols, w, dt):
+        # a bottleneck of a few columns: the CUDA-core product reads them where they lie; a wide one is copied out
+        return ops.gemm_simt(cols, w, dt) if cols.shape[1] < 64 else ops.linear(cols.contiguous(), w, dt)
+
+    def forward(self, h, step, cache):
+        dt = self.runtime.dtype
+        GN, HP, H, C = self.G * self.N, self.H * self.P, self.H, self.conv_channels
+        proj = ops.linear(h, self.w_h, dt)
+        qkv = ops.causal_conv(proj[:, :C], self.conv_w, None, cache.state[:, self.n_state:], step)
+        b_raw = proj[:, C:C + H]
+        a1, g1 = proj[:, C + H:C + H + self.r_a], proj[:, C + H + self.r_a:]
+        z = self._narrow_product(a1, self.w_a2, dt)
+        gate = self._narrow_product(g1, self.w_g2, dt)
+        qn, kn, qk, decay, beta = ops.delta_prep(qkv[:, :GN], qkv[:, GN:2 * GN], z, b_raw, self.a_log, self.dt_bias,
+                                                 self.l2_eps, self.N ** -0.5, H, self.N, heads_per_group=H // self.G)
+        o = ops.delta_scan(qn, kn, qk, decay, beta, qkv[:, 2 * GN:], cache.state[:, :self.n_state], step, H, self.N,
+                           self.P, heads_per_group=H // self.G)
+        gated = ops.gated_norm(o, dt, weight=self.norm_w, eps=self.eps, group=self.P, weight_per_group=True, gate=gate,
+                               gate_mode=ops.GATE_AFTER_NORM, activation="sigmoid")
+        return ops.linear(gated, self.w_o, torch.float32, defer=True)

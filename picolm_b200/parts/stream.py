@@ -67,6 +67,30 @@ class ResidualStream:
         self.narrowed = True
 
 
+def pending_addends(p):
+    """A pending delta as the addends a kernel that folds it into the stream takes: (rows or a product that has not
+    run, bias vector or None, weight of the delta's own RMS norm or None, that norm's eps)."""
+    if isinstance(p, PostNormed):
+        return p.delta, None, p.norm.weight_f32(), float(p.norm.params["eps"])
+    if isinstance(p, BiasedDelta):
+        return p.delta, p.bias, None, 0.0
+    return p, None, None, 0.0
+
+
+def settle(stream: "ResidualStream", dtype, vec: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None):
+    """Add what is pending (and, if given, the float32 vector `vec` [d] and the float32 rows `extra` [T, d]) to the
+    stream; returns the sum in `dtype` (None: returns nothing).  For parts that read the stream itself, not a norm
+    of it."""
+    from .. import ops
+    p = stream.pending
+    if vec is not None and isinstance(p, BiasedDelta):
+        p = p.compute()                       # one vector a pass
+    delta, bias, post_w, post_eps = pending_addends(p)
+    stream.pending = None
+    return ops.dyt_norm(stream.x, dtype, delta=delta, delta_bias=bias if vec is None else vec, post_weight=post_w,
+                        post_eps=post_eps, extra=extra)
+
+
 def _narrowed(p, rows):
     """The pending delta `p` at the rows `rows` only."""
     from .. import ops
