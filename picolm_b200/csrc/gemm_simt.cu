@@ -9,8 +9,11 @@
 // matrix mode) and the any-size product of the bfloat16 path when a shape does
 // not fit the tensor-core kernel.  Each output element is accumulated over k in
 // ascending order by one thread, so a row's result never depends on which other
-// rows are in the batch.
+// rows are in the batch.  With all three types float32 the sum of each piece of BK terms is folded into a
+// double: the error of a long dot product then stays that of a short one (a recurrence that keeps a state for
+// thousands of tokens multiplies what its gates' sums lose).
 #include "common.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -25,11 +28,16 @@ gemm_simt_kernel(const Ta* __restrict__ A, const Tw* __restrict__ W, To* __restr
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = tid / 16, tx = tid % 16;
+    constexpr bool kWide = std::is_same<Ta, float>::value && std::is_same<Tw, float>::value && std::is_same<To, float>::value;
     float acc[4][4];
+    double wide[kWide ? 4 : 1][kWide ? 4 : 1];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.f;
+            if (kWide) wide[kWide ? i : 0][kWide ? j : 0] = 0.0;
+        }
 
     for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
@@ -53,7 +61,22 @@ gemm_simt_kernel(const Ta* __restrict__ A, const Tw* __restrict__ W, To* __restr
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
+        if (kWide) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    wide[kWide ? i : 0][kWide ? j : 0] += (double)acc[i][j];
+                    acc[i][j] = 0.f;
+                }
+        }
         __syncthreads();
+    }
+    if (kWide) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = (float)wide[kWide ? i : 0][kWide ? j : 0];
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

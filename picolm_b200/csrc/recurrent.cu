@@ -13,6 +13,7 @@
 // Everything that enters a recurrence is fp32: decays, step sizes, the state, the sums.  T is the run's
 // element type (float or bf16) of projections and activations; small parameter vectors are fp32.
 #include "common.cuh"
+#include <type_traits>
 
 #define SCAN_THREADS 128
 #define SCAN_PTILE 32
@@ -862,7 +863,9 @@ extern "C" int plm_store_rows_paged(const void* rows, int dtype, long ld, void* 
 //   zr = Wr[b] u_b + br,  zi = Wi[b] u_b + bi   (Wr[b], Wi[b] square, [out, in])
 //   log a = -sigmoid(zr) * rate,  a = exp(log a),  x = sqrt(1 - a^2) * sigmoid(zi) * u
 // with rate = 8 softplus(lambda) worked out once by the host.  1 - a^2 is taken as -expm1(2 log a), which keeps its
-// digits where a is close to 1.  The sums are fp32 and run over k in ascending order for every element.
+// digits where a is close to 1, and what is handed on is log a, not a: a float next to 1 has lost the digits of
+// 1 - a, on which a state that lasts thousands of tokens depends.  The sums are fp32 and run over k in ascending order for every element; with float32
+// inputs each piece of 32 terms is folded into a double (a decay close to 1 multiplies what its gate's sum loses).
 // One block: 32 tokens x 32 channels of one gate block, K in pieces of 32 through shared memory.
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -878,7 +881,9 @@ rglru_gates_kernel(const T* __restrict__ u, long ldu, const Tw* __restrict__ wr,
     pdl_wait();
     const int t0 = blockIdx.x * 32, blk = blockIdx.y, o0 = blockIdx.z * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    constexpr bool kWide = std::is_same<T, float>::value;
     float zr[4] = {0.f, 0.f, 0.f, 0.f}, zi[4] = {0.f, 0.f, 0.f, 0.f};
+    double zr_w[4] = {0.0, 0.0, 0.0, 0.0}, zi_w[4] = {0.0, 0.0, 0.0, 0.0};
     for (int k0 = 0; k0 < n; k0 += 32) {
         const int kk = k0 + tx;
 #pragma unroll
@@ -901,7 +906,18 @@ rglru_gates_kernel(const T* __restrict__ u, long ldu, const Tw* __restrict__ wr,
                 zi[j] = fmaf(b, uv, zi[j]);
             }
         }
+        if (kWide) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                zr_w[j] += (double)zr[j], zi_w[j] += (double)zi[j];
+                zr[j] = zi[j] = 0.f;
+            }
+        }
         __syncthreads();
+    }
+    if (kWide) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) zr[j] = (float)zr_w[j], zi[j] = (float)zi_w[j];
     }
     const int o = o0 + tx;
     if (o >= n) return;
@@ -913,7 +929,7 @@ rglru_gates_kernel(const T* __restrict__ u, long ldu, const Tw* __restrict__ wr,
         if (tt >= n_tokens) continue;
         const float uu = to_f32<T>(u[(long)tt * ldu + c]);
         const float la = -sigmoid_f(zr[j] + b_r) * rt;
-        a_out[(long)tt * W + c] = expf(la);
+        a_out[(long)tt * W + c] = la;
         x_out[(long)tt * W + c] = sqrtf(-expm1f(2.f * la)) * sigmoid_f(zi[j] + b_i) * uu;
     }
 }
@@ -934,7 +950,9 @@ extern "C" int plm_rglru_gates(const void* u, int dtype, long ldu, const void* w
     return PLM_ERR_DTYPE;
 }
 
-// S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens, out_t = S_t * gelu_tanh(y_t + y_bias).  One block
+// S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens, out_t = S_t * gelu_tanh(y_t + y_bias), with a_t given
+// as its logarithm.  a_t is taken as 1 + expm1(log a_t) in double and S is walked in double, so that neither a decay
+// next to 1 nor a long prompt loses digits; the state is kept in the cache as float32.  One block
 // per (32 channels, sequence): its 32 warps take 32 equal stretches of the sequence's tokens; a first walk leaves each
 // stretch's product of decays and its own sum, one warp chains them from the cache's state, a second walk writes.
 template <typename T>
@@ -942,7 +960,7 @@ __global__ void __launch_bounds__(1024)
 diag_scan_kernel(const float* __restrict__ a, const float* __restrict__ x, const T* __restrict__ yraw, long ldy,
                  const float* __restrict__ ybias, float* __restrict__ state, long state_stride, T* __restrict__ out,
                  const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int W) {
-    __shared__ float As[32][33], Bs[32][33];
+    __shared__ double As[32][33], Bs[32][33];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y, lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
@@ -951,11 +969,11 @@ diag_scan_kernel(const float* __restrict__ a, const float* __restrict__ x, const
     if (s1 <= s0) return;
     const int L = (s1 - s0 + 31) / 32;
     const int t0 = min(s1, s0 + seg * L), t1 = min(s1, t0 + L);
-    float A = 1.f, Bv = 0.f;
+    double A = 1.0, Bv = 0.0;
     if (c < W)
         for (int t = t0; t < t1; ++t) {
-            const float av = a[(long)t * W + c];
-            Bv = fmaf(av, Bv, x[(long)t * W + c]);
+            const double av = 1.0 + (double)expm1f(a[(long)t * W + c]);
+            Bv = fma(av, Bv, (double)x[(long)t * W + c]);
             A *= av;
         }
     As[seg][lane] = A;
@@ -963,21 +981,21 @@ diag_scan_kernel(const float* __restrict__ a, const float* __restrict__ x, const
     __syncthreads();
     if (seg == 0 && c < W) {
         float* st = state + (long)seq_slot[b] * state_stride;
-        float carry = st[c];
+        double carry = (double)st[c];
         for (int s = 0; s < 32; ++s) {
-            const float sa = As[s][lane], sb = Bs[s][lane];
+            const double sa = As[s][lane], sb = Bs[s][lane];
             As[s][lane] = carry;
-            carry = fmaf(sa, carry, sb);
+            carry = fma(sa, carry, sb);
         }
-        st[c] = carry;
+        st[c] = (float)carry;
     }
     __syncthreads();
     if (c >= W) return;
-    float S = As[seg][lane];
+    double S = As[seg][lane];
     const float yb = ybias ? ybias[c] : 0.f;
     for (int t = t0; t < t1; ++t) {
-        S = fmaf(a[(long)t * W + c], S, x[(long)t * W + c]);
-        out[(long)t * W + c] = from_f32<T>(S * gelu_tanh_f(to_f32<T>(yraw[(long)t * ldy + c]) + yb));
+        S = fma(1.0 + (double)expm1f(a[(long)t * W + c]), S, (double)x[(long)t * W + c]);
+        out[(long)t * W + c] = from_f32<T>((float)S * gelu_tanh_f(to_f32<T>(yraw[(long)t * ldy + c]) + yb));
     }
 }
 
@@ -992,7 +1010,7 @@ __global__ void diag_scan_decode_kernel(const float* __restrict__ a, const float
     if (idx >= (long)n_seqs * W) return;
     const int b = (int)(idx / W), c = (int)(idx % W);
     float* st = state + (long)seq_slot[b] * state_stride;
-    const float S = fmaf(a[idx], st[c], x[idx]);
+    const float S = (float)fma(1.0 + (double)expm1f(a[idx]), (double)st[c], (double)x[idx]);
     st[c] = S;
     out[idx] = from_f32<T>(S * gelu_tanh_f(to_f32<T>(yraw[(long)b * ldy + c]) + (ybias ? ybias[c] : 0.f)));
 }
@@ -1022,8 +1040,9 @@ extern "C" int plm_diag_scan(const float* a, const float* x, const void* yraw, i
 // ------------------------------------------------------------------------------------------------ gated delta rule
 // What the delta rule's recurrence takes, worked out per token in fp32 from the convolved projections:
 //   qn = q / sqrt(sum q^2 + l2_eps) * q_scale and kn = k / sqrt(sum k^2 + l2_eps) per key head, qk = qn . kn,
-//   dec[h, n] = exp(-exp(A_log[h]) * softplus(z[h, n] + dt_bias[h, n])),  beta[h] = sigmoid(braw[h]).
-// One block per token; a warp per key head, then per head.
+//   dec[h, n] = expm1(-exp(A_log[h]) * softplus(z[h, n] + dt_bias[h, n])),  beta[h] = sigmoid(braw[h]).
+// dec is the decay minus one: a decay next to 1 keeps the digits of its distance from 1, which a state that lasts long
+// depends on, and the recurrence takes S + dec S.  One block per token; a warp per key head, then per head.
 template <typename T>
 __global__ void __launch_bounds__(128)
 delta_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ z, long ldz,
@@ -1056,7 +1075,7 @@ delta_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
             const float rate = expf(a_log[h]);
             const T* zr = z + (long)t * ldz + (long)h * N;
             float* d = dec + ((long)t * H + h) * N;
-            for (int i = lane; i < N; i += 32) d[i] = expf(-rate * softplus_f(to_f32<T>(zr[i]) + dt_bias[(long)h * N + i]));
+            for (int i = lane; i < N; i += 32) d[i] = expm1f(-rate * softplus_f(to_f32<T>(zr[i]) + dt_bias[(long)h * N + i]));
             if (lane == 0) beta[(long)t * H + h] = sigmoid_f(to_f32<T>(braw[(long)t * ldb + h]));
         }
     }
@@ -1079,7 +1098,8 @@ extern "C" int plm_delta_prep(const void* q, long ldq, const void* k, long ldk, 
 }
 
 // The delta rule per head, token by token, state S [N, P] in fp32:
-//   S <- diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  (the read-out sees the write).
+//   S <- S + diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  (the read-out sees the write;
+//   dec_t is the decay minus one).
 // The columns of S do not meet, so a block takes 32 of them for one (sequence, head): a warp holds 8 columns, the N rows of
 // a column are dealt to 4 lanes (row n with lane n % 4), NR values of the state a thread.  Both sums over the rows,
 // k . (dec S) and q . (dec S), are taken in one pass before the write, and o = q . (dec S) + (q . k) u.
@@ -1126,7 +1146,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             const bool in = n < N;
             qs[idx] = in ? qn[(row * G + g) * N + n] : 0.f;
             ks[idx] = in ? kn[(row * G + g) * N + n] : 0.f;
-            gs[idx] = in ? dec[(row * H + h) * N + n] : 1.f;
+            gs[idx] = in ? dec[(row * H + h) * N + n] : 0.f;
         }
         for (int idx = threadIdx.x; idx < nt * DELTA_COLS; idx += 128) {
             const int tt = idx / DELTA_COLS, cc = idx - tt * DELTA_COLS;
@@ -1145,7 +1165,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             float d1 = 0.f, d2 = 0.f;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
-                const float s = S[r] * gt[r * 4];
+                const float s = fmaf(S[r], gt[r * 4], S[r]);
                 S[r] = s;
                 d1 = fmaf(kt[r * 4], s, d1);
                 d2 = fmaf(qt[r * 4], s, d2);

@@ -222,9 +222,10 @@ def rglru_gates(u: torch.Tensor, w_rate: torch.Tensor, w_in: torch.Tensor, b_rat
     """The two gates of a real-gated diagonal recurrence from its convolved input `u` [T, W] (a column slice will
     do): the channels come in `blocks` equal parts, each with square matrices `w_rate[b]`, `w_in[b]` ([blocks, n, n],
     [out, in], of u's type) and biases [W] float32;
-      a = exp(-sigmoid(w_rate[b] u_b + b_rate) * rate),   x = sqrt(1 - a^2) * sigmoid(w_in[b] u_b + b_in) * u
+      log a = -sigmoid(w_rate[b] u_b + b_rate) * rate,   x = sqrt(1 - a^2) * sigmoid(w_in[b] u_b + b_in) * u
     with `rate` [W] float32 (the constant times softplus of the learned parameter).  Sums and everything behind
-    them in float32; returns (a, x), float32 [T, W] each."""
+    them in float32; returns (log a, x), float32 [T, W] each: the logarithm, because a float next to 1 no longer
+    says how far from 1 it is."""
     ldu = _cols(u, "u")
     T, W = u.shape
     if blocks <= 0 or W % blocks:
@@ -246,8 +247,8 @@ def rglru_gates(u: torch.Tensor, w_rate: torch.Tensor, w_in: torch.Tensor, b_rat
 
 def diag_scan(a: torch.Tensor, x: torch.Tensor, y_raw: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
               step) -> torch.Tensor:
-    """S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens (float32 `a`, `x` [T, W], contiguous), from
-    and into `state` (float32 [slots, >= W], contiguous rows); returns S_t * gelu_tanh(y_raw_t + y_bias) as [T, W] of
+    """S_t = a_t S_(t-1) + x_t per channel over each sequence's tokens (float32 `a`, `x` [T, W], contiguous; `a` holds
+    the decays' logarithms), from and into `state` (float32 [slots, >= W], contiguous rows); returns S_t * gelu_tanh(y_raw_t + y_bias) as [T, W] of
     y_raw's type (`y_raw` may be a column slice; `y_bias` [W] float32 or None)."""
     T, W = a.shape
     for t, n in ((a, "a"), (x, "x")):
@@ -275,8 +276,8 @@ def delta_prep(q: torch.Tensor, k: torch.Tensor, z: torch.Tensor, b_raw: torch.T
                dt_bias: torch.Tensor, l2_eps: float, q_scale: float, heads: int, key_dim: int, heads_per_group: int = 1):
     """What the gated delta rule's recurrence takes, per token in float32 from the convolved projections (all of one
     type, column slices will do): q, k [T, groups * key_dim] made unit vectors per group (`x / sqrt(sum x^2 +
-    l2_eps)`, q also times `q_scale`), their product q . k, the decays `exp(-exp(a_log[h]) softplus(z + dt_bias))`
-    for z [T, heads * key_dim], and `sigmoid(b_raw)` for b_raw [T, heads].  Returns (qn, kn, qk, decay, beta)."""
+    l2_eps)`, q also times `q_scale`), their product q . k, the decays minus one `expm1(-exp(a_log[h]) softplus(z + dt_bias))`
+    for z [T, heads * key_dim] (minus one: a decay next to 1 keeps its distance from 1), and `sigmoid(b_raw)` for b_raw [T, heads].  Returns (qn, kn, qk, decay, beta)."""
     T = q.shape[0]
     H, N = heads, key_dim
     if H % heads_per_group:
@@ -304,8 +305,8 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, qk: torch.Tensor, decay: torc
                v: torch.Tensor, state: torch.Tensor, step, heads: int, key_dim: int, value_dim: int,
                heads_per_group: int = 1) -> torch.Tensor:
     """The gated delta rule over each sequence's tokens, per head, state S [key_dim, value_dim] in float32:
-      S <- diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
-    (the read-out sees the token's own write).  qn, kn, qk, decay, beta as `delta_prep` returns them; v [T, heads *
+      S <- S + diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+    (the read-out sees the token's own write).  qn, kn, qk, decay (the decay minus one), beta as `delta_prep` returns them; v [T, heads *
     value_dim] (a column slice will do); `state` float32 [slots, >= heads * key_dim * value_dim] with contiguous
     rows holds S as [heads, key_dim, value_dim] and is carried on.  Returns o, float32 [T, heads * value_dim]."""
     H, N, P = heads, key_dim, value_dim

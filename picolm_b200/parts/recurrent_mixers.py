@@ -208,8 +208,8 @@ class GatedDiagonalRecurrence(_StateMixer):
         yx = ops.linear(h, self.w_yx, dt)
         u = ops.causal_conv(yx[:, W:], self.conv_w, self.conv_b, cache.state[:, W:], step, in_bias=self.x_bias,
                             activation=None)
-        a, x = ops.rglru_gates(u, self.w_ra, self.w_ri, self.b_ra, self.b_ri, self.rate, self.blocks)
-        g = ops.diag_scan(a, x, yx[:, :W], self.y_bias, cache.state[:, :W], step)
+        log_a, x = ops.rglru_gates(u, self.w_ra, self.w_ri, self.b_ra, self.b_ri, self.rate, self.blocks)
+        g = ops.diag_scan(log_a, x, yx[:, :W], self.y_bias, cache.state[:, :W], step)
         return ops.linear(g, self.w_o, torch.float32, defer=True)
 
 
