@@ -1,7 +1,8 @@
-"""Throughput of another design (Potuzen, Kunulorn) beside the Llama decoder at equal layer sizes (random weights): prefill
+"""Throughput of another design (Potuzen, Kunulorn, Tebasun) beside the Llama decoder (Tebasun: beside Potuzen, the other
+design whose layers are recurrences and attention in turn) at equal layer sizes (random weights): prefill
 tokens/s of one prompt and decode tokens/s of a batch, at a few sizes that resemble a real model's layers,
 and, with `kernels=True`, the device time of every kind of launch with the fraction of the memory's or the
-tensor cores' measured rate that it reaches.  `bench.py --design potuzen|kunulorn` calls this."""
+tensor cores' measured rate that it reaches.  `bench.py --design potuzen|kunulorn|tebasun` calls this."""
 from __future__ import annotations
 
 import json
@@ -52,6 +53,22 @@ def kunulorn_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict
         out.append({"type": "attention", "mixer": m, "mlp": mlp})
     return {"architecture": "Kunulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
             "embedding": {"scale": float(width) ** 0.5}, "layers": out}
+
+
+def tebasun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
+    """`layers` runs of the schedule: a gated diagonal recurrence as wide as the model first and last, and between
+    them layers of attention (heads of 128, a sink, half of each head rotated with stretched frequencies) beside a
+    gated delta rule (heads of 128 x 128); a dense feed-forward in every layer; the second and third layer run twice."""
+    rglru = {"type": "rglru", "mixer": {"width": width, "blocks": width // 256, "conv": 4}, "mlp": {"kind": "dense", "ff": ff}}
+    left = {"heads": width // 128, "kv_heads": width // 512, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": width // 256, "kv_heads": width // 512, "dim": 128, "vdim": 128, "conv": 4, "rank": 16}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.5},
+                "mlp": {"kind": "dense", "ff": ff}}
+    n = layers - 2                                             # the looped pair is counted twice
+    return {"architecture": "Tebasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [rglru if i in (0, n - 1) else parallel for i in range(n)]}
 
 
 def llama_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict:
@@ -141,18 +158,23 @@ def _table(rows, top=14):
 
 
 def run(design: str, sizes, prompt_tokens: int, batch: int, steps: int, warmup: int, kernels: bool) -> dict:
-    if design not in ("potuzen", "kunulorn"):
-        raise ValueError(f"no design {design!r} to compare (known: potuzen, kunulorn)")
-    result = {"design": design, "beside": "LlamaForCausalLM", "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+    if design not in ("potuzen", "kunulorn", "tebasun"):
+        raise ValueError(f"no design {design!r} to compare (known: potuzen, kunulorn, tebasun)")
+    beside = "potuzen" if design == "tebasun" else "llama"
+    result = {"design": design, "beside": "Potuzen" if beside == "potuzen" else "LlamaForCausalLM", "dtype": "bf16",
+              "data": "synthetic (random weights and tokens)",
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "steps": steps, "warmup": warmup, "sizes": {}}
     for name in sizes:
         width, ff, layers, vocab, heads = SIZES[name]
         t0 = time.time()
-        config = potuzen_config(width, ff, layers, vocab) if design == "potuzen" else kunulorn_config(width, ff, layers, vocab, heads)
+        config = {"potuzen": lambda: potuzen_config(width, ff, layers, vocab),
+                  "kunulorn": lambda: kunulorn_config(width, ff, layers, vocab, heads),
+                  "tebasun": lambda: tebasun_config(width, ff, layers, vocab)}[design]()
         ours = _measure(config, prompt_tokens, batch, steps, warmup, kernels)
-        twin = _measure(llama_config(width, ff, layers, vocab, heads), prompt_tokens, batch, steps, warmup, kernels)
+        twin_config = potuzen_config(width, ff, layers, vocab) if beside == "potuzen" else llama_config(width, ff, layers, vocab, heads)
+        twin = _measure(twin_config, prompt_tokens, batch, steps, warmup, kernels)
         result["sizes"][name] = {
-            "width": width, "ff": ff, "layers": layers, design: ours, "llama": twin,
+            "width": width, "ff": ff, "layers": layers, design: ours, beside: twin,
             "prefill_ratio": round(ours["prefill_tokens_per_s"] / twin["prefill_tokens_per_s"], 3),
             "decode_ratio": round(ours["decode_tokens_per_s"] / twin["decode_tokens_per_s"], 3)}
         print(f"[bench] {name}: {time.time() - t0:.0f} s", file=sys.stderr)

@@ -1040,9 +1040,9 @@ extern "C" int plm_diag_scan(const float* a, const float* x, const void* yraw, i
 // ------------------------------------------------------------------------------------------------ gated delta rule
 // What the delta rule's recurrence takes, worked out per token in fp32 from the convolved projections:
 //   qn = q / sqrt(sum q^2 + l2_eps) * q_scale and kn = k / sqrt(sum k^2 + l2_eps) per key head, qk = qn . kn,
-//   dec[h, n] = expm1(-exp(A_log[h]) * softplus(z[h, n] + dt_bias[h, n])),  beta[h] = sigmoid(braw[h]).
-// dec is the decay minus one: a decay next to 1 keeps the digits of its distance from 1, which a state that lasts long
-// depends on, and the recurrence takes S + dec S.  One block per token; a warp per key head, then per head.
+//   dec[h, n] = -exp(A_log[h]) * softplus(z[h, n] + dt_bias[h, n]),  beta[h] = sigmoid(braw[h]).
+// dec is the decay's logarithm: a float next to 1 has lost the digits of its distance from 1, which a state that lasts
+// long depends on; the recurrence takes S + expm1(dec) S.  One block per token; a warp per key head, then per head.
 template <typename T>
 __global__ void __launch_bounds__(128)
 delta_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ z, long ldz,
@@ -1075,7 +1075,7 @@ delta_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ k, lo
             const float rate = expf(a_log[h]);
             const T* zr = z + (long)t * ldz + (long)h * N;
             float* d = dec + ((long)t * H + h) * N;
-            for (int i = lane; i < N; i += 32) d[i] = expm1f(-rate * softplus_f(to_f32<T>(zr[i]) + dt_bias[(long)h * N + i]));
+            for (int i = lane; i < N; i += 32) d[i] = -rate * softplus_f(to_f32<T>(zr[i]) + dt_bias[(long)h * N + i]);
             if (lane == 0) beta[(long)t * H + h] = sigmoid_f(to_f32<T>(braw[(long)t * ldb + h]));
         }
     }
@@ -1098,8 +1098,8 @@ extern "C" int plm_delta_prep(const void* q, long ldq, const void* k, long ldk, 
 }
 
 // The delta rule per head, token by token, state S [N, P] in fp32:
-//   S <- S + diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  (the read-out sees the write;
-//   dec_t is the decay minus one).
+//   S <- S + diag(expm1(dec_t)) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t  (the read-out sees the
+//   write; dec_t is the decay's logarithm).
 // The columns of S do not meet, so a block takes 32 of them for one (sequence, head): a warp holds 8 columns, the N rows of
 // a column are dealt to 4 lanes (row n with lane n % 4), NR values of the state a thread.  Both sums over the rows,
 // k . (dec S) and q . (dec S), are taken in one pass before the write, and o = q . (dec S) + (q . k) u.
@@ -1146,7 +1146,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             const bool in = n < N;
             qs[idx] = in ? qn[(row * G + g) * N + n] : 0.f;
             ks[idx] = in ? kn[(row * G + g) * N + n] : 0.f;
-            gs[idx] = in ? dec[(row * H + h) * N + n] : 0.f;
+            gs[idx] = in ? expm1f(dec[(row * H + h) * N + n]) : 0.f;
         }
         for (int idx = threadIdx.x; idx < nt * DELTA_COLS; idx += 128) {
             const int tt = idx / DELTA_COLS, cc = idx - tt * DELTA_COLS;
@@ -1222,4 +1222,254 @@ extern "C" int plm_delta_scan(const float* qn, const float* kn, const float* qk,
     if (nr <= 48) DS(48);
     DS(64);
 #undef DS
+}
+
+// ------------------------------------------------------------------------------------- gated delta rule, chunk by chunk
+// The same recurrence for prompts, DELTA_CHUNK tokens at a time.  With L_t the running sum of the decays' logarithms
+// inside a chunk (per head and key channel) and S_0 the state the chunk starts from,
+//   u_t = beta_t (v_t - S_0^T (k_t e^{L_t}) - sum_{s<t} A_ts u_s),   A_ts = sum_n k_tn k_sn e^{L_tn - L_sn}
+//   o_t = S_0^T (q_t e^{L_t}) + sum_{s<=t} M_ts u_s,                 M_ts = sum_n q_tn k_sn e^{L_tn - L_sn}
+//   S_C = diag(e^{L_C}) S_0 + sum_s (k_s e^{L_C - L_s}) u_s^T
+// Every exponent is <= 0: nothing is divided by a running decay, so no choice of decays overflows.  What does not depend
+// on the state (the three scaled copies of k and q, A, M, e^{L_C}) is made for all chunks side by side by a first
+// kernel; the second walks a sequence's chunks with the state in registers: two passes of dot products without a chain
+// between tokens, a forward substitution over the chunk's tokens, and the state's update.
+#define DELTA_CHUNK 32
+
+__host__ __device__ static inline long delta_ws_floats(int NP) { return 3L * DELTA_CHUNK * NP + 2L * DELTA_CHUNK * DELTA_CHUNK + NP; }
+
+// The width of a row of keys in the workspace: four quarters of the NR values a thread of the second kernel holds.
+static inline int delta_chunk_np(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256; }
+
+// grid (chunk of the sequence, sequence, head).  ws per (slot, head): Kp [C][NP] | Qp [C][NP] | Ke [C][NP] | A [C][C] | M [C][C]
+// | e^{L_C} [NP], NP = delta_chunk_np(N), the padding zero.  A sequence's chunk c lives in slot seq_start / C + sequence + c.
+__global__ void __launch_bounds__(256)
+delta_chunk_prep_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ lgd,
+                        float* __restrict__ ws, const int* __restrict__ seq_start, int H, int N, int NP, int heads_per_group) {
+    constexpr int C = DELTA_CHUNK;
+    extern __shared__ __align__(16) float smem[];
+    float* cum = smem;                  // [C][N]
+    float* ks = cum + (long)C * N;
+    float* qs = ks + (long)C * N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    const int s0 = seq_start[b], s1 = seq_start[b + 1];
+    const int t0 = s0 + c * C;
+    if (t0 >= s1) return;
+    const int nt = min(C, s1 - t0);
+    const int G = H / heads_per_group, g = h / heads_per_group;
+    const long slot = (long)(s0 / C) + b + c;
+    for (int idx = threadIdx.x; idx < C * N; idx += 256) {
+        const int tt = idx / N, n = idx - tt * N;
+        const bool in = tt < nt;
+        const long row = t0 + tt;
+        ks[idx] = in ? kn[(row * G + g) * N + n] : 0.f;
+        qs[idx] = in ? qn[(row * G + g) * N + n] : 0.f;
+        cum[idx] = in ? lgd[(row * H + h) * N + n] : 0.f;
+    }
+    __syncthreads();
+    for (int n = threadIdx.x; n < N; n += 256) {
+        float acc = 0.f;
+        for (int tt = 0; tt < C; ++tt) {
+            acc += cum[tt * N + n];
+            cum[tt * N + n] = acc;
+        }
+    }
+    __syncthreads();
+    float* out = ws + (slot * H + h) * delta_ws_floats(NP);
+    float* Kp = out;
+    float* Qp = Kp + (long)C * NP;
+    float* Ke = Qp + (long)C * NP;
+    float* A = Ke + (long)C * NP;
+    float* M = A + C * C;
+    float* ge = M + C * C;
+    for (int idx = threadIdx.x; idx < C * NP; idx += 256) {
+        const int tt = idx / NP, n = idx - tt * NP;
+        float kp = 0.f, qp = 0.f, ke = 0.f;
+        if (n < N) {
+            const float l = cum[tt * N + n], e = expf(l), kv = ks[tt * N + n];
+            kp = kv * e;
+            qp = qs[tt * N + n] * e;
+            ke = kv * expf(cum[(C - 1) * N + n] - l);
+        }
+        Kp[idx] = kp, Qp[idx] = qp, Ke[idx] = ke;
+    }
+    for (int n = threadIdx.x; n < NP; n += 256) ge[n] = n < N ? expf(cum[(C - 1) * N + n]) : 0.f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = warp; i < C * C; i += 8) {
+        const int t = i / C, s = i - t * C;
+        if (s > t) continue;
+        float a = 0.f, m = 0.f;
+        for (int n = lane; n < N; n += 32) {
+            const float kk = ks[s * N + n] * expf(cum[t * N + n] - cum[s * N + n]);
+            a = fmaf(ks[t * N + n], kk, a);
+            m = fmaf(qs[t * N + n], kk, m);
+        }
+        a = warp_sum(a), m = warp_sum(m);
+        if (lane == 0) A[i] = a, M[i] = m;
+    }
+}
+
+// grid: (sequence, head, 32 columns of the state).  A warp holds 8 columns; the N rows of a column are dealt to 4 lanes
+// in contiguous quarters, NR values of the state a thread.
+template <int NR>
+__global__ void __launch_bounds__(128)
+delta_chunk_scan_kernel(const float* __restrict__ ws, const float* __restrict__ beta, const void* __restrict__ v, int v_f32, long ldv,
+                        float* __restrict__ state, long state_stride, float* __restrict__ y, const int* __restrict__ seq_start,
+                        const int* __restrict__ seq_slot, int H, int N, int P) {
+    constexpr int C = DELTA_CHUNK, NP = NR * 4, SEG = NR + 4, RS = 4 * SEG;      // SEG: a quarter's floats in a row, padded
+    extern __shared__ __align__(16) float smem[];
+    float* Kp = smem;                    // [C][RS]
+    float* Qp = Kp + C * RS;
+    float* Ke = Qp + C * RS;
+    float* A = Ke + C * RS;              // [C][C]
+    float* M = A + C * C;
+    float* ge = M + C * C;               // [RS]
+    float* vs = ge + RS;                 // [C][DELTA_COLS]
+    float* bs = vs + C * DELTA_COLS;     // [C]
+    pdl_launch_dependents();
+    const int ptiles = (P + DELTA_COLS - 1) / DELTA_COLS;
+    int bid = blockIdx.x;
+    const int ptile = bid % ptiles;
+    bid /= ptiles;
+    const int h = bid % H, b = bid / H;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = (warp << 3) + (lane & 7), part = lane >> 3;
+    const int p = ptile * DELTA_COLS + col;
+    pdl_wait();
+    const int s0 = seq_start[b], s1 = seq_start[b + 1];
+    if (s1 <= s0) return;
+    float* st = state + (long)seq_slot[b] * state_stride + (long)h * N * P;
+    float S[NR];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int n = part * NR + j;
+        S[j] = (n < N && p < P) ? st[(long)n * P + p] : 0.f;
+    }
+    const long wsf = 3L * C * NP + 2L * C * C + NP;
+    const long slot0 = (long)(s0 / C) + b;
+    int chunk = 0;
+    for (int base = s0; base < s1; base += C, ++chunk) {
+        const int nt = min(C, s1 - base);
+        const float* src = ws + ((slot0 + chunk) * H + h) * wsf;
+        __syncthreads();
+        constexpr int ROW4 = NP / 4, MAT4 = C * ROW4;
+        for (int idx = threadIdx.x; idx < 3 * MAT4; idx += 128) {
+            const int m = idx / MAT4, rem = idx - m * MAT4;
+            const int tt = rem / ROW4, n4 = (rem - tt * ROW4) * 4;
+            const int prt = n4 / NR, j = n4 - prt * NR;
+            *reinterpret_cast<float4*>(smem + m * C * RS + tt * RS + prt * SEG + j) =
+                *reinterpret_cast<const float4*>(src + (long)m * C * NP + (long)tt * NP + n4);
+        }
+        for (int idx = threadIdx.x; idx < 2 * C * C / 4; idx += 128)
+            reinterpret_cast<float4*>(A)[idx] = reinterpret_cast<const float4*>(src + 3L * C * NP)[idx];
+        for (int idx = threadIdx.x; idx < ROW4; idx += 128) {
+            const int n4 = idx * 4, prt = n4 / NR, j = n4 - prt * NR;
+            *reinterpret_cast<float4*>(ge + prt * SEG + j) = *reinterpret_cast<const float4*>(src + 3L * C * NP + 2L * C * C + n4);
+        }
+        for (int idx = threadIdx.x; idx < C * DELTA_COLS; idx += 128) {
+            const int tt = idx / DELTA_COLS, cc = idx - tt * DELTA_COLS;
+            const int pp = ptile * DELTA_COLS + cc;
+            const long at = (long)(base + tt) * ldv + (long)h * P + pp;
+            vs[idx] = (tt < nt && pp < P) ? (v_f32 ? static_cast<const float*>(v)[at] : to_f32<bf16>(static_cast<const bf16*>(v)[at])) : 0.f;
+        }
+        if (threadIdx.x < C) bs[threadIdx.x] = threadIdx.x < nt ? beta[(long)(base + threadIdx.x) * H + h] : 0.f;
+        __syncthreads();
+        float r[C], o[C];
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            const float4* kp = reinterpret_cast<const float4*>(Kp + t * RS + part * SEG);
+            const float4* qp = reinterpret_cast<const float4*>(Qp + t * RS + part * SEG);
+            float ra = 0.f, oa = 0.f;
+#pragma unroll
+            for (int j4 = 0; j4 < NR / 4; ++j4) {
+                const float4 a = kp[j4], q = qp[j4];
+                ra = fmaf(a.x, S[4 * j4], ra), ra = fmaf(a.y, S[4 * j4 + 1], ra);
+                ra = fmaf(a.z, S[4 * j4 + 2], ra), ra = fmaf(a.w, S[4 * j4 + 3], ra);
+                oa = fmaf(q.x, S[4 * j4], oa), oa = fmaf(q.y, S[4 * j4 + 1], oa);
+                oa = fmaf(q.z, S[4 * j4 + 2], oa), oa = fmaf(q.w, S[4 * j4 + 3], oa);
+            }
+            ra += __shfl_xor_sync(0xffffffffu, ra, 8);
+            oa += __shfl_xor_sync(0xffffffffu, oa, 8);
+            ra += __shfl_xor_sync(0xffffffffu, ra, 16);
+            oa += __shfl_xor_sync(0xffffffffu, oa, 16);
+            r[t] = vs[t * DELTA_COLS + col] - ra;
+            o[t] = oa;
+        }
+        // forward substitution: r[t] becomes u_t
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            const float u = bs[t] * r[t];
+            r[t] = u;
+#pragma unroll
+            for (int t2 = t + 1; t2 < C; ++t2) r[t2] = fmaf(-A[t2 * C + t], u, r[t2]);
+        }
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            float acc = o[t];
+#pragma unroll
+            for (int s = 0; s <= t; ++s) acc = fmaf(M[t * C + s], r[s], acc);
+            if (part == 0 && p < P && t < nt) y[(long)(base + t) * H * P + (long)h * P + p] = acc;
+        }
+#pragma unroll
+        for (int j = 0; j < NR; ++j) S[j] *= ge[part * SEG + j];
+#pragma unroll
+        for (int s = 0; s < C; ++s) {
+            const float4* ke = reinterpret_cast<const float4*>(Ke + s * RS + part * SEG);
+            const float u = r[s];
+#pragma unroll
+            for (int j4 = 0; j4 < NR / 4; ++j4) {
+                const float4 e = ke[j4];
+                S[4 * j4] = fmaf(e.x, u, S[4 * j4]), S[4 * j4 + 1] = fmaf(e.y, u, S[4 * j4 + 1]);
+                S[4 * j4 + 2] = fmaf(e.z, u, S[4 * j4 + 2]), S[4 * j4 + 3] = fmaf(e.w, u, S[4 * j4 + 3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int n = part * NR + j;
+        if (n < N && p < P) st[(long)n * P + p] = S[j];
+    }
+}
+
+template <int NR>
+static int delta_chunk_launch(const float* ws, const float* beta, const void* v, int v_f32, long ldv, float* state, long state_stride,
+                              float* y, const int* seq_start, const int* seq_slot, int n_seqs, int H, int N, int P,
+                              cudaStream_t stream) {
+    constexpr int C = DELTA_CHUNK, RS = 4 * (NR + 4);
+    const size_t smem = ((size_t)3 * C * RS + 2 * C * C + RS + C * DELTA_COLS + C) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_chunk_scan_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const unsigned grid = (unsigned)((long)n_seqs * H * ((P + DELTA_COLS - 1) / DELTA_COLS));
+    return plm_status_of(launch_pdl(delta_chunk_scan_kernel<NR>, dim3(grid), dim3(128), smem, stream, ws, beta, v, v_f32,
+                                    ldv, state, state_stride, y, seq_start, seq_slot, H, N, P));
+}
+
+// ws: ((n_tokens / DELTA_CHUNK) + n_seqs + 1) * H * delta_ws_floats(delta_chunk_np(N)) floats.
+extern "C" int plm_delta_chunk_scan(const float* qn, const float* kn, const float* dec, const float* beta, const void* v,
+                                    int dtype, long ldv, float* state, long state_stride, float* y, float* ws,
+                                    const int* seq_start, const int* seq_slot, int n_seqs, int max_new, int H, int N, int P,
+                                    int heads_per_group, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return PLM_OK;
+    if (H <= 0 || N <= 0 || P <= 0 || heads_per_group <= 0 || H % heads_per_group) return PLM_ERR_SHAPE;
+    if (N > 256) return PLM_ERR_UNSUPPORTED;
+    if (dtype != PLM_F32 && dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    const int NP = delta_chunk_np(N);
+    const size_t prep_smem = (size_t)3 * DELTA_CHUNK * N * sizeof(float);
+    if (prep_smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prep_smem);
+    const dim3 pgrid((unsigned)((max_new + DELTA_CHUNK - 1) / DELTA_CHUNK), (unsigned)n_seqs, (unsigned)H);
+    int e = plm_status_of(launch_pdl(delta_chunk_prep_kernel, pgrid, dim3(256), prep_smem, stream, qn, kn, dec, ws, seq_start, H, N,
+                                     NP, heads_per_group));
+    if (e != PLM_OK) return e;
+#define DCS(NR_)                                                                                                          \
+    return delta_chunk_launch<NR_>(ws, beta, v, dtype == PLM_F32 ? 1 : 0, ldv, state, state_stride, y, seq_start, seq_slot, n_seqs, \
+                                   H, N, P, stream)
+    if (NP <= 16) DCS(4);
+    if (NP <= 32) DCS(8);
+    if (NP <= 64) DCS(16);
+    if (NP <= 128) DCS(32);
+    DCS(64);
+#undef DCS
 }

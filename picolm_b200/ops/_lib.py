@@ -68,6 +68,7 @@ _SIGNATURES = {
     "plm_rglru_gates": [_vp, _i, _l, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "plm_diag_scan": [_vp, _vp, _vp, _i, _l, _vp, _vp, _l, _vp, _vp, _vp, _i, _i, _i, _vp],
     "plm_delta_prep": [_vp, _l, _vp, _l, _vp, _l, _vp, _l, _i, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "plm_delta_chunk_scan": [_vp, _vp, _vp, _vp, _vp, _i, _l, _vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "plm_delta_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _l, _vp, _l, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_linear_scan": [_vp, _vp, _vp, _vp, _i, _l, _l, _l, _l, _i, _vp, _vp, _vp, _f, _f, _vp, _l, _vp, _l, _vp, _vp,
                         _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],

@@ -272,12 +272,23 @@ def diag_scan(a: torch.Tensor, x: torch.Tensor, y_raw: torch.Tensor, y_bias: Opt
     return out
 
 
+DELTA_CHUNK_FROM = 16      # tokens of a step's longest sequence from which the delta rule runs chunk by chunk
+
+
+def delta_chunk_workspace(n_tokens: int, n_seqs: int, heads: int, key_dim: int) -> int:
+    """Floats of workspace the chunked delta rule takes (as the kernels lay it out): per chunk and head three copies
+    of the chunk's keys or queries [32, NP], two matrices [32, 32] and a row [NP], NP the key size rounded up to the
+    next of 16, 32, 64, 128, 256; a sequence's chunks start at slot seq_start // 32 + its number."""
+    np_ = next(w for w in (16, 32, 64, 128, 256) if key_dim <= w)
+    return (n_tokens // 32 + n_seqs + 1) * heads * (3 * 32 * np_ + 2 * 32 * 32 + np_)
+
+
 def delta_prep(q: torch.Tensor, k: torch.Tensor, z: torch.Tensor, b_raw: torch.Tensor, a_log: torch.Tensor,
                dt_bias: torch.Tensor, l2_eps: float, q_scale: float, heads: int, key_dim: int, heads_per_group: int = 1):
     """What the gated delta rule's recurrence takes, per token in float32 from the convolved projections (all of one
     type, column slices will do): q, k [T, groups * key_dim] made unit vectors per group (`x / sqrt(sum x^2 +
-    l2_eps)`, q also times `q_scale`), their product q . k, the decays minus one `expm1(-exp(a_log[h]) softplus(z + dt_bias))`
-    for z [T, heads * key_dim] (minus one: a decay next to 1 keeps its distance from 1), and `sigmoid(b_raw)` for b_raw [T, heads].  Returns (qn, kn, qk, decay, beta)."""
+    l2_eps)`, q also times `q_scale`), their product q . k, the decays' logarithms `-exp(a_log[h]) softplus(z + dt_bias)`
+    for z [T, heads * key_dim] (the logarithm: a decay next to 1 keeps its distance from 1), and `sigmoid(b_raw)` for b_raw [T, heads].  Returns (qn, kn, qk, decay, beta)."""
     T = q.shape[0]
     H, N = heads, key_dim
     if H % heads_per_group:
@@ -305,10 +316,13 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, qk: torch.Tensor, decay: torc
                v: torch.Tensor, state: torch.Tensor, step, heads: int, key_dim: int, value_dim: int,
                heads_per_group: int = 1) -> torch.Tensor:
     """The gated delta rule over each sequence's tokens, per head, state S [key_dim, value_dim] in float32:
-      S <- S + diag(decay_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
-    (the read-out sees the token's own write).  qn, kn, qk, decay (the decay minus one), beta as `delta_prep` returns them; v [T, heads *
+      S <- diag(exp(decay_t)) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+    (the read-out sees the token's own write).  qn, kn, qk, decay (its logarithm), beta as `delta_prep` returns them; v [T, heads *
     value_dim] (a column slice will do); `state` float32 [slots, >= heads * key_dim * value_dim] with contiguous
-    rows holds S as [heads, key_dim, value_dim] and is carried on.  Returns o, float32 [T, heads * value_dim]."""
+    rows holds S as [heads, key_dim, value_dim] and is carried on.  Returns o, float32 [T, heads * value_dim].
+    A step whose longest sequence brings `DELTA_CHUNK_FROM` tokens or more runs chunk by chunk (two kernels: what does
+    not depend on the state for all chunks side by side, then a walk over each sequence's chunks); shorter portions
+    and single tokens run token by token."""
     H, N, P = heads, key_dim, value_dim
     T = v.shape[0]
     if H % heads_per_group:
@@ -328,6 +342,16 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, qk: torch.Tensor, decay: torc
         raise KernelError("delta_scan: the state must be float32 with heads * key_dim * value_dim values a row")
     y = torch.empty((T, H * P), dtype=torch.float32, device=v.device)
     set_bounds("recurrent", n_seqs=step.n_seqs, device=v.device)
+    if step.max_new >= DELTA_CHUNK_FROM and not (step.is_decode and step.n_tokens == step.n_seqs):
+        floats = delta_chunk_workspace(T, step.n_seqs, H, N)
+        ws = torch.empty((floats,), dtype=torch.float32, device=v.device)
+        _check(_fn("recurrent", "plm_delta_chunk_scan")(
+            _p(qn), _p(kn), _p(decay), _p(beta), _p(v), _dt(v, "v"), ldv, _p(state), lds, _p(y), _p(ws), _p(step.seq_start),
+            _p(step.seq_slot), step.n_seqs, int(step.max_new), H, N, P, heads_per_group, _stream()),
+            f"delta_chunk_scan T={T} H={H} N={N} P={P}", kernels=2,
+            nbytes=2 * floats * 4 + T * H * P * (4 + v.element_size()) + 2 * step.n_seqs * H * N * P * 4,
+            flops=T * H * (6 * N * P + 6 * 32 * N + 4 * 32 * P))
+        return y
     _check(_fn("recurrent", "plm_delta_scan")(
         _p(qn), _p(kn), _p(qk), _p(decay), _p(beta), _p(v), _dt(v, "v"), ldv, _p(state), lds, _p(y), _p(step.seq_start),
         _p(step.seq_slot), step.n_seqs, H, N, P, heads_per_group, _stream()), f"delta_scan T={T} H={H} N={N} P={P}",

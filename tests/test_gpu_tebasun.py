@@ -226,7 +226,7 @@ def test_delta_rule_kernels(dtype, N, Pv, H, hpg):
     dev = "cuda:0"
     g = torch.Generator().manual_seed(N * 7 + Pv)
     G = H // hpg
-    total = [37, 6, 20]
+    total = [37 + 96, 6, 20 + 64]        # the first portion runs chunk by chunk (several chunks, the last ragged)
     mk = lambda t, c: torch.randn(t, c + 8, generator=g).to(dtype)
     q, k, v = [mk(t, G * N) for t in total], [mk(t, G * N) for t in total], [mk(t, H * Pv) for t in total]
     z, braw = [mk(t, H * N) for t in total], [mk(t, H) for t in total]
@@ -248,7 +248,7 @@ def test_delta_rule_kernels(dtype, N, Pv, H, hpg):
     slots = [3, 0, 1]
     got, at = [[] for _ in total], [0, 0, 0]
     cu = lambda t: t.to(dev).contiguous()
-    for cut in ([20, 2, 9], [1, 1, 1], [2, 2, 2], [1, 1, 1], [13, 0, 7]):
+    for cut in ([20 + 96, 2, 9 + 64], [1, 1, 1], [2, 2, 2], [1, 1, 1], [13, 0, 7]):
         live = [i for i, c in enumerate(cut) if c]
         step = _Step([cut[i] for i in live], [slots[i] for i in live], dev)
         rows = lambda src: torch.cat([src[i][at[i]:at[i] + cut[i]] for i in live]).to(dev)
@@ -409,7 +409,7 @@ def test_requests_that_end_at_page_borders_in_one_batch(tmp_path):
     lens = [63, 64, 65, 128, 129, 1]
     reqs = [random_tokens(n + 4, VOCAB, 30 + n) for n in lens]
     eng = _engine(d)
-    for _ in range(2):                                # the second round takes the pages and slots the first gave back
+    for _ in range(2):                                # the second time takes the pages and slots the first gave back
         outs = run_batch(eng, reqs, lens)
         for got, r in zip(outs, reqs):
             _close(got, _plain(tensors, config, r), what=f"a request of {len(r)} tokens")
