@@ -1238,10 +1238,10 @@ extern "C" int plm_delta_scan(const float* qn, const float* kn, const float* qk,
 
 __host__ __device__ static inline long delta_ws_floats(int NP) { return 3L * DELTA_CHUNK * NP + 2L * DELTA_CHUNK * DELTA_CHUNK + NP; }
 
-// The width of a row of keys in the workspace: four quarters of the NR values a thread of the second kernel holds.
-static inline int delta_chunk_np(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256; }
+// The width of a row of keys in the workspace: eight times the NR values a thread of the second kernel holds.
+static inline int delta_chunk_np(int N) { return N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256; }
 
-// grid (chunk of the sequence, sequence, head).  ws per (slot, head): Kp [C][NP] | Qp [C][NP] | Ke [C][NP] | A [C][C] | M [C][C]
+// grid (chunk of the sequence, sequence, head).  ws per (slot, head): Kp [C][NP] | Qp [C][NP] | Ke [C][NP] | A^T [C][C] | M^T [C][C]
 // | e^{L_C} [NP], NP = delta_chunk_np(N), the padding zero.  A sequence's chunk c lives in slot seq_start / C + sequence + c.
 __global__ void __launch_bounds__(256)
 delta_chunk_prep_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ lgd,
@@ -1297,46 +1297,49 @@ delta_chunk_prep_kernel(const float* __restrict__ qn, const float* __restrict__ 
     }
     for (int n = threadIdx.x; n < NP; n += 256) ge[n] = n < N ? expf(cum[(C - 1) * N + n]) : 0.f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // both stored transposed, [s][t], so that lanes that hold different t read different banks; zero where s > t (A: s >= t)
     for (int i = warp; i < C * C; i += 8) {
         const int t = i / C, s = i - t * C;
-        if (s > t) continue;
         float a = 0.f, m = 0.f;
-        for (int n = lane; n < N; n += 32) {
-            const float kk = ks[s * N + n] * expf(cum[t * N + n] - cum[s * N + n]);
-            a = fmaf(ks[t * N + n], kk, a);
-            m = fmaf(qs[t * N + n], kk, m);
+        if (s <= t) {
+            for (int n = lane; n < N; n += 32) {
+                const float kk = ks[s * N + n] * expf(cum[t * N + n] - cum[s * N + n]);
+                a = fmaf(ks[t * N + n], kk, a);
+                m = fmaf(qs[t * N + n], kk, m);
+            }
+            a = warp_sum(a), m = warp_sum(m);
         }
-        a = warp_sum(a), m = warp_sum(m);
-        if (lane == 0) A[i] = a, M[i] = m;
+        if (lane == 0) A[s * C + t] = s < t ? a : 0.f, M[s * C + t] = m;
     }
 }
 
-// grid: (sequence, head, 32 columns of the state).  A warp holds 8 columns; the N rows of a column are dealt to 4 lanes
-// in contiguous quarters, NR values of the state a thread.
-template <int NR>
+// grid: (sequence, head, DELTA_CCOLS columns of the state).  A warp holds 4 columns; the N rows of a column are dealt to 8
+// lanes in contiguous eighths, NR values of the state a thread.  A chunk's matrices come through cp.async into one of
+// STAGES buffers, the next chunk's while this one is worked on.
+#define DELTA_CCOLS 16
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int NR, int STAGES>
 __global__ void __launch_bounds__(128)
 delta_chunk_scan_kernel(const float* __restrict__ ws, const float* __restrict__ beta, const void* __restrict__ v, int v_f32, long ldv,
                         float* __restrict__ state, long state_stride, float* __restrict__ y, const int* __restrict__ seq_start,
                         const int* __restrict__ seq_slot, int H, int N, int P) {
-    constexpr int C = DELTA_CHUNK, NP = NR * 4, SEG = NR + 4, RS = 4 * SEG;      // SEG: a quarter's floats in a row, padded
+    constexpr int C = DELTA_CHUNK, NP = NR * 8, SEG = NR + 4, RS = 8 * SEG;      // SEG: an eighth's floats in a row, padded
+    constexpr int STAGE = 3 * C * RS + 2 * C * C + RS;                            // Kp | Qp | Ke [C][RS], A | M [C][C], e^{L_C} [RS]
     extern __shared__ __align__(16) float smem[];
-    float* Kp = smem;                    // [C][RS]
-    float* Qp = Kp + C * RS;
-    float* Ke = Qp + C * RS;
-    float* A = Ke + C * RS;              // [C][C]
-    float* M = A + C * C;
-    float* ge = M + C * C;               // [RS]
-    float* vs = ge + RS;                 // [C][DELTA_COLS]
-    float* bs = vs + C * DELTA_COLS;     // [C]
+    float* vs = smem + STAGES * STAGE;   // [C][DELTA_CCOLS]
+    float* bs = vs + C * DELTA_CCOLS;    // [C]
     pdl_launch_dependents();
-    const int ptiles = (P + DELTA_COLS - 1) / DELTA_COLS;
+    const int ptiles = (P + DELTA_CCOLS - 1) / DELTA_CCOLS;
     int bid = blockIdx.x;
     const int ptile = bid % ptiles;
     bid /= ptiles;
     const int h = bid % H, b = bid / H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int col = (warp << 3) + (lane & 7), part = lane >> 3;
-    const int p = ptile * DELTA_COLS + col;
+    const int col = (warp << 2) + (lane & 3), part = lane >> 2;
+    const int p = ptile * DELTA_CCOLS + col;
     pdl_wait();
     const int s0 = seq_start[b], s1 = seq_start[b + 1];
     if (s1 <= s0) return;
@@ -1348,83 +1351,122 @@ delta_chunk_scan_kernel(const float* __restrict__ ws, const float* __restrict__ 
         S[j] = (n < N && p < P) ? st[(long)n * P + p] : 0.f;
     }
     const long wsf = 3L * C * NP + 2L * C * C + NP;
-    const long slot0 = (long)(s0 / C) + b;
-    int chunk = 0;
-    for (int base = s0; base < s1; base += C, ++chunk) {
-        const int nt = min(C, s1 - base);
-        const float* src = ws + ((slot0 + chunk) * H + h) * wsf;
-        __syncthreads();
+    const float* src0 = ws + (((long)(s0 / C) + b) * H + h) * wsf;
+    const int n_chunks = (s1 - s0 + C - 1) / C;
+    auto fetch = [&](int chunk, int stage) {
+        const float* src = src0 + (long)chunk * H * wsf;
+        float* dst = smem + stage * STAGE;
         constexpr int ROW4 = NP / 4, MAT4 = C * ROW4;
         for (int idx = threadIdx.x; idx < 3 * MAT4; idx += 128) {
             const int m = idx / MAT4, rem = idx - m * MAT4;
             const int tt = rem / ROW4, n4 = (rem - tt * ROW4) * 4;
             const int prt = n4 / NR, j = n4 - prt * NR;
-            *reinterpret_cast<float4*>(smem + m * C * RS + tt * RS + prt * SEG + j) =
-                *reinterpret_cast<const float4*>(src + (long)m * C * NP + (long)tt * NP + n4);
+            cp_async16(dst + m * C * RS + tt * RS + prt * SEG + j, src + (long)m * C * NP + (long)tt * NP + n4);
         }
-        for (int idx = threadIdx.x; idx < 2 * C * C / 4; idx += 128)
-            reinterpret_cast<float4*>(A)[idx] = reinterpret_cast<const float4*>(src + 3L * C * NP)[idx];
+        for (int idx = threadIdx.x; idx < 2 * C * C / 4; idx += 128) cp_async16(dst + 3 * C * RS + idx * 4, src + 3L * C * NP + idx * 4);
         for (int idx = threadIdx.x; idx < ROW4; idx += 128) {
             const int n4 = idx * 4, prt = n4 / NR, j = n4 - prt * NR;
-            *reinterpret_cast<float4*>(ge + prt * SEG + j) = *reinterpret_cast<const float4*>(src + 3L * C * NP + 2L * C * C + n4);
+            cp_async16(dst + 3 * C * RS + 2 * C * C + prt * SEG + j, src + 3L * C * NP + 2L * C * C + n4);
         }
-        for (int idx = threadIdx.x; idx < C * DELTA_COLS; idx += 128) {
-            const int tt = idx / DELTA_COLS, cc = idx - tt * DELTA_COLS;
-            const int pp = ptile * DELTA_COLS + cc;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (STAGES == 2) fetch(0, 0);
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        const int base = s0 + chunk * C, nt = min(C, s1 - base);
+        const int stage = STAGES == 2 ? (chunk & 1) : 0;
+        if (STAGES == 2) {
+            if (chunk + 1 < n_chunks) {
+                fetch(chunk + 1, stage ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+        } else {
+            fetch(chunk, 0);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        for (int idx = threadIdx.x; idx < C * DELTA_CCOLS; idx += 128) {
+            const int tt = idx / DELTA_CCOLS, cc = idx - tt * DELTA_CCOLS;
+            const int pp = ptile * DELTA_CCOLS + cc;
             const long at = (long)(base + tt) * ldv + (long)h * P + pp;
             vs[idx] = (tt < nt && pp < P) ? (v_f32 ? static_cast<const float*>(v)[at] : to_f32<bf16>(static_cast<const bf16*>(v)[at])) : 0.f;
         }
         if (threadIdx.x < C) bs[threadIdx.x] = threadIdx.x < nt ? beta[(long)(base + threadIdx.x) * H + h] : 0.f;
         __syncthreads();
+        const float* Kp = smem + stage * STAGE;
+        const float* Qp = Kp + C * RS;
+        const float* Ke = Qp + C * RS;
+        const float* A = Ke + C * RS;
+        const float* M = A + C * C;
+        const float* ge = M + C * C;
+        // this lane's share of both dot products for every token of the chunk
         float r[C], o[C];
 #pragma unroll
         for (int t = 0; t < C; ++t) {
             const float4* kp = reinterpret_cast<const float4*>(Kp + t * RS + part * SEG);
             const float4* qp = reinterpret_cast<const float4*>(Qp + t * RS + part * SEG);
-            float ra = 0.f, oa = 0.f;
+            float ra0 = 0.f, ra1 = 0.f, oa0 = 0.f, oa1 = 0.f;
 #pragma unroll
             for (int j4 = 0; j4 < NR / 4; ++j4) {
                 const float4 a = kp[j4], q = qp[j4];
-                ra = fmaf(a.x, S[4 * j4], ra), ra = fmaf(a.y, S[4 * j4 + 1], ra);
-                ra = fmaf(a.z, S[4 * j4 + 2], ra), ra = fmaf(a.w, S[4 * j4 + 3], ra);
-                oa = fmaf(q.x, S[4 * j4], oa), oa = fmaf(q.y, S[4 * j4 + 1], oa);
-                oa = fmaf(q.z, S[4 * j4 + 2], oa), oa = fmaf(q.w, S[4 * j4 + 3], oa);
+                ra0 = fmaf(a.x, S[4 * j4], ra0), ra1 = fmaf(a.y, S[4 * j4 + 1], ra1);
+                ra0 = fmaf(a.z, S[4 * j4 + 2], ra0), ra1 = fmaf(a.w, S[4 * j4 + 3], ra1);
+                oa0 = fmaf(q.x, S[4 * j4], oa0), oa1 = fmaf(q.y, S[4 * j4 + 1], oa1);
+                oa0 = fmaf(q.z, S[4 * j4 + 2], oa0), oa1 = fmaf(q.w, S[4 * j4 + 3], oa1);
             }
-            ra += __shfl_xor_sync(0xffffffffu, ra, 8);
-            oa += __shfl_xor_sync(0xffffffffu, oa, 8);
-            ra += __shfl_xor_sync(0xffffffffu, ra, 16);
-            oa += __shfl_xor_sync(0xffffffffu, oa, 16);
-            r[t] = vs[t * DELTA_COLS + col] - ra;
-            o[t] = oa;
+            r[t] = ra0 + ra1;
+            o[t] = oa0 + oa1;
         }
-        // forward substitution: r[t] becomes u_t
+        // The eight lanes of a column add their shares so that lane `part` ends with the sums of tokens 4 part .. 4 part + 3
+        // (three rounds, each handing half of what is left to the partner): r[0..3], o[0..3].
+#pragma unroll
+        for (int half = C / 2, mask = 16; half >= 4; half >>= 1, mask >>= 1) {
+            const bool upper = (lane & mask) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float sr = upper ? r[i] : r[i + half], so = upper ? o[i] : o[i + half];
+                const float kr = upper ? r[i + half] : r[i], ko = upper ? o[i + half] : o[i];
+                r[i] = kr + __shfl_xor_sync(0xffffffffu, sr, mask);
+                o[i] = ko + __shfl_xor_sync(0xffffffffu, so, mask);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = vs[(part * 4 + j) * DELTA_CCOLS + col] - r[j];
+        // forward substitution: the owner of token t makes u_t and hands it to the column's other lanes; every lane
+        // keeps all of u and takes u_t out of the tokens it owns (A^T is zero where they are not later than t)
+        float u[C];
 #pragma unroll
         for (int t = 0; t < C; ++t) {
-            const float u = bs[t] * r[t];
-            r[t] = u;
+            u[t] = __shfl_sync(0xffffffffu, bs[t] * r[t & 3], ((t >> 2) << 2) + (lane & 3));
+            const float* at = A + t * C + part * 4;
 #pragma unroll
-            for (int t2 = t + 1; t2 < C; ++t2) r[t2] = fmaf(-A[t2 * C + t], u, r[t2]);
+            for (int j = 0; j < 4; ++j) r[j] = fmaf(-at[j], u[t], r[j]);
         }
+        {
+            float acc[4] = {o[0], o[1], o[2], o[3]};
 #pragma unroll
-        for (int t = 0; t < C; ++t) {
-            float acc = o[t];
+            for (int s = 0; s < C; ++s) {
+                const float* mt = M + s * C + part * 4;
 #pragma unroll
-            for (int s = 0; s <= t; ++s) acc = fmaf(M[t * C + s], r[s], acc);
-            if (part == 0 && p < P && t < nt) y[(long)(base + t) * H * P + (long)h * P + p] = acc;
+                for (int j = 0; j < 4; ++j) acc[j] = fmaf(mt[j], u[s], acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (p < P && part * 4 + j < nt) y[(long)(base + part * 4 + j) * H * P + (long)h * P + p] = acc[j];
         }
 #pragma unroll
         for (int j = 0; j < NR; ++j) S[j] *= ge[part * SEG + j];
 #pragma unroll
         for (int s = 0; s < C; ++s) {
             const float4* ke = reinterpret_cast<const float4*>(Ke + s * RS + part * SEG);
-            const float u = r[s];
 #pragma unroll
             for (int j4 = 0; j4 < NR / 4; ++j4) {
                 const float4 e = ke[j4];
-                S[4 * j4] = fmaf(e.x, u, S[4 * j4]), S[4 * j4 + 1] = fmaf(e.y, u, S[4 * j4 + 1]);
-                S[4 * j4 + 2] = fmaf(e.z, u, S[4 * j4 + 2]), S[4 * j4 + 3] = fmaf(e.w, u, S[4 * j4 + 3]);
+                S[4 * j4] = fmaf(e.x, u[s], S[4 * j4]), S[4 * j4 + 1] = fmaf(e.y, u[s], S[4 * j4 + 1]);
+                S[4 * j4 + 2] = fmaf(e.z, u[s], S[4 * j4 + 2]), S[4 * j4 + 3] = fmaf(e.w, u[s], S[4 * j4 + 3]);
             }
         }
+        __syncthreads();
     }
 #pragma unroll
     for (int j = 0; j < NR; ++j) {
@@ -1433,16 +1475,16 @@ delta_chunk_scan_kernel(const float* __restrict__ ws, const float* __restrict__ 
     }
 }
 
-template <int NR>
+template <int NR, int STAGES>
 static int delta_chunk_launch(const float* ws, const float* beta, const void* v, int v_f32, long ldv, float* state, long state_stride,
                               float* y, const int* seq_start, const int* seq_slot, int n_seqs, int H, int N, int P,
                               cudaStream_t stream) {
-    constexpr int C = DELTA_CHUNK, RS = 4 * (NR + 4);
-    const size_t smem = ((size_t)3 * C * RS + 2 * C * C + RS + C * DELTA_COLS + C) * sizeof(float);
+    constexpr int C = DELTA_CHUNK, RS = 8 * (NR + 4);
+    const size_t smem = ((size_t)STAGES * (3 * C * RS + 2 * C * C + RS) + C * DELTA_CCOLS + C) * sizeof(float);
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(delta_chunk_scan_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    const unsigned grid = (unsigned)((long)n_seqs * H * ((P + DELTA_COLS - 1) / DELTA_COLS));
-    return plm_status_of(launch_pdl(delta_chunk_scan_kernel<NR>, dim3(grid), dim3(128), smem, stream, ws, beta, v, v_f32,
+        cudaFuncSetAttribute(delta_chunk_scan_kernel<NR, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const unsigned grid = (unsigned)((long)n_seqs * H * ((P + DELTA_CCOLS - 1) / DELTA_CCOLS));
+    return plm_status_of(launch_pdl(delta_chunk_scan_kernel<NR, STAGES>, dim3(grid), dim3(128), smem, stream, ws, beta, v, v_f32,
                                     ldv, state, state_stride, y, seq_start, seq_slot, H, N, P));
 }
 
@@ -1463,13 +1505,12 @@ extern "C" int plm_delta_chunk_scan(const float* qn, const float* kn, const floa
     int e = plm_status_of(launch_pdl(delta_chunk_prep_kernel, pgrid, dim3(256), prep_smem, stream, qn, kn, dec, ws, seq_start, H, N,
                                      NP, heads_per_group));
     if (e != PLM_OK) return e;
-#define DCS(NR_)                                                                                                          \
-    return delta_chunk_launch<NR_>(ws, beta, v, dtype == PLM_F32 ? 1 : 0, ldv, state, state_stride, y, seq_start, seq_slot, n_seqs, \
-                                   H, N, P, stream)
-    if (NP <= 16) DCS(4);
-    if (NP <= 32) DCS(8);
-    if (NP <= 64) DCS(16);
-    if (NP <= 128) DCS(32);
-    DCS(64);
+#define DCS(NR_, ST_)                                                                                                     \
+    return delta_chunk_launch<NR_, ST_>(ws, beta, v, dtype == PLM_F32 ? 1 : 0, ldv, state, state_stride, y, seq_start, seq_slot, \
+                                        n_seqs, H, N, P, stream)
+    if (NP <= 32) DCS(4, 2);
+    if (NP <= 64) DCS(8, 2);
+    if (NP <= 128) DCS(16, 2);
+    DCS(32, 1);
 #undef DCS
 }

@@ -278,8 +278,8 @@ DELTA_CHUNK_FROM = 16      # tokens of a step's longest sequence from which the 
 def delta_chunk_workspace(n_tokens: int, n_seqs: int, heads: int, key_dim: int) -> int:
     """Floats of workspace the chunked delta rule takes (as the kernels lay it out): per chunk and head three copies
     of the chunk's keys or queries [32, NP], two matrices [32, 32] and a row [NP], NP the key size rounded up to the
-    next of 16, 32, 64, 128, 256; a sequence's chunks start at slot seq_start // 32 + its number."""
-    np_ = next(w for w in (16, 32, 64, 128, 256) if key_dim <= w)
+    next of 32, 64, 128, 256; a sequence's chunks start at slot seq_start // 32 + its number."""
+    np_ = next(w for w in (32, 64, 128, 256) if key_dim <= w)
     return (n_tokens // 32 + n_seqs + 1) * heads * (3 * 32 * np_ + 2 * 32 * 32 + np_)
 
 
