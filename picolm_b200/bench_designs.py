@@ -58,16 +58,17 @@ def kunulorn_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict
 def tebasun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
     """`layers` runs of the schedule: a gated diagonal recurrence as wide as the model first and last, and between
     them layers of attention (heads of 128, a sink, half of each head rotated with stretched frequencies) beside a
-    gated delta rule (heads of 128 x 128); a dense feed-forward in every layer; the second and third layer run twice."""
+    gated delta rule (heads of 128 x 128); a dense feed-forward in every layer; the second and third layer (the second alone of fewer than six) run twice."""
     rglru = {"type": "rglru", "mixer": {"width": width, "blocks": width // 256, "conv": 4}, "mlp": {"kind": "dense", "ff": ff}}
     left = {"heads": width // 128, "kv_heads": width // 512, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
             "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     right = {"heads": width // 256, "kv_heads": width // 512, "dim": 128, "vdim": 128, "conv": 4, "rank": 16}
     parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.5},
                 "mlp": {"kind": "dense", "ff": ff}}
-    n = layers - 2                                             # the looped pair is counted twice
+    looped = 2 if layers >= 6 else 1                           # these layers are counted twice
+    n = layers - looped
     return {"architecture": "Tebasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
-            "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 3, "times": 2},
+            "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 1 + looped, "times": 2},
             "layers": [rglru if i in (0, n - 1) else parallel for i in range(n)]}
 
 
