@@ -58,9 +58,9 @@ def _config(layers, width=40, loop=None, side=6, eps=1e-5, emb_scale=1.7):
     return out
 
 
-def _make(tmp_path, name, config, seed, slow=False):
+def _make(tmp_path, name, config, seed, slow=False, sink=None):
     """A model folder with random weights for `config`; returns (folder, plain tensors, config).  `slow`: the decays
-    of both recurrences are drawn close to 1."""
+    of both recurrences are drawn close to 1.  `sink`: every head's sink is this number (else drawn from N(0, 2))."""
     from picolm_b200.config import config_from_dict
     from picolm_b200.weights import random_tensors, save_safetensors
     cfg = config_from_dict(config)
@@ -69,7 +69,7 @@ def _make(tmp_path, name, config, seed, slow=False):
     for n in list(tensors):
         t = tensors[n]
         if n.endswith(".sink"):
-            tensors[n] = (2.0 * torch.randn(t.shape, generator=g)).to(t.dtype)
+            tensors[n] = (torch.full(t.shape, float(sink)) if sink is not None else 2.0 * torch.randn(t.shape, generator=g)).to(t.dtype)
         elif slow and n.endswith(".mix.lam"):
             tensors[n] = (-9.0 + 2.0 * torch.rand(t.shape, generator=g)).to(t.dtype)
         elif slow and n.endswith(".A_log"):
@@ -324,6 +324,11 @@ def test_float32_model_matches_plain_in_every_cut(tmp_path, name):
         _close(got, want[id(t)], what="batch of unequal requests")
     # slots and pages that were used are used again, and give the same
     _close(run_whole(eng, a), want[id(a)], what="whole, again")
+    # few rows wanted: the last layer narrows the stream after its mixer, and the token input finds the rows' tokens
+    s = eng.new_sequence()
+    got = eng.step([(s, a)], [[149, 3]]).float().cpu()
+    eng.end_sequence(s)
+    _close(got, want[id(a)][[149, 3]], what="two rows of a prompt")
     eng.cache.check()
     assert eng.cache.slots.used == 0 and all(g.pool.used == 0 for g in eng.cache.kv_groups)
 
@@ -446,6 +451,29 @@ def test_bfloat16_follows_the_plain_implementation(tmp_path):
         rel = ((got - whole).double().pow(2).mean().sqrt() / want.double().std()).item()
         assert rel < 0.03, f"two cuts of the same request differ by {rel:.3f} of the spread"
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dim,heads,kv", [(64, 4, 2), (128, 2, 1), (96, 3, 3), (40, 2, 1)])
+def test_bfloat16_sink_attention_on_the_tensor_cores(tmp_path, dim, heads, kv):
+    """Head sizes that the bfloat16 attention kernels take on the tensor cores (tcgen05 prompts at 64 and 128, mma.sync
+    prompts and decode steps at the other multiples of 16, heads padded to the next one at 40), with the sink and with
+    keys that serve as values: without the sink the exact logits differ by several times what bfloat16 costs, so a
+    kernel that forgot it would show; prompts, portions and single tokens agree."""
+    layers = [_parallel(heads=heads, kv_heads=kv, dim=dim, rot=_rot(dims=dim // 2), scale=1.5 * dim ** -0.5, right_scale=0.3,
+                        left_scale=1.5, ff=None)]
+    d, tensors, config = _make(tmp_path, f"tc{dim}", _config(layers, width=64, side=None), seed=dim, sink=5.0)
+    t = random_tokens(200, VOCAB, dim)
+    want = _plain(tensors, config, t)
+    none = dict(tensors, **{"l0.mix.left.sink": torch.full_like(tensors["l0.mix.left.sink"], -60.0)})
+    gap = ((_plain(none, config, t) - want).double().pow(2).mean().sqrt() / want.double().std()).item()
+    assert gap > 0.15, f"the weights do not let the sink show ({gap:.3f})"
+    eng = _engine(d, dtype="bfloat16")
+    whole = run_whole(eng, t)
+    rel = ((whole - want).double().pow(2).mean().sqrt() / want.double().std()).item()
+    assert rel < 0.05, f"bfloat16 logits are {rel:.3f} of the spread away from the exact ones"
+    for got in (run_tail(eng, t, tail=70), run_chunks(eng, t, [64, 2, 134]), run_batch(eng, [t[:9], t], [5, 130])[1]):
+        rel = ((got - whole).double().pow(2).mean().sqrt() / want.double().std()).item()
+        assert rel < 0.03, f"two cuts of the same request differ by {rel:.3f} of the spread"
 
 
 # ---------------------------------------------------------------------------------------------- generation
