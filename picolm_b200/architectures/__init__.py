@@ -1,3 +1,3 @@
 """Architectures known to the library.  Importing this package registers them;
 a new one is a new module here that calls `register_architecture`."""
-from . import kunulorn, llama, potuzen, tebasun  # noqa: F401
+from . import fupapel, kunulorn, llama, potuzen, tebasun  # noqa: F401

@@ -21,6 +21,9 @@ class CacheSpec:
     values: bool = True                         # kv: False = one row per position that serves as key and as value
     shape: Tuple[int, ...] = ()                 # state: per-sequence shape
     dtype: str = "float32"                      # state: element type
+    # True: a layer that reads another layer's caches still keeps this one itself (what it makes of its own input:
+    # a convolution's tail, the row before), and a layer that lends its caches does not lend this one
+    private: bool = False
 
     @staticmethod
     def kv(num_kv_heads: int, head_dim: int, window: Optional[int] = None, values: bool = True) -> "CacheSpec":
@@ -31,8 +34,8 @@ class CacheSpec:
         return CacheSpec("kv", num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, values=bool(values))
 
     @staticmethod
-    def state(shape, dtype: str = "float32") -> "CacheSpec":
-        return CacheSpec("state", shape=tuple(int(s) for s in shape), dtype=dtype)
+    def state(shape, dtype: str = "float32", private: bool = False) -> "CacheSpec":
+        return CacheSpec("state", shape=tuple(int(s) for s in shape), dtype=dtype, private=bool(private))
 
     def group_key(self):
         return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.shape, self.dtype, self.values)

@@ -33,12 +33,14 @@ class LayerSpec:
     "feed_forward_norm" and "feed_forward"; another arrangement may want four
     norms, one, or two mixers).  The value of a name is `(family, PartSpec)`.
     `cache_of` names another layer whose caches this layer's parts read instead
-    of owning their own (they then write nothing)."""
+    of owning their own (they then write nothing).  `params` holds constants of
+    the arrangement itself (a factor on what the layer adds to the stream)."""
 
     prefix: str
     arrangement: str
     parts: Mapping[str, Tuple[str, PartSpec]]
     cache_of: Optional[int] = None
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def part(self, name: str) -> PartSpec:
         """The spec of the part the arrangement calls `name`."""

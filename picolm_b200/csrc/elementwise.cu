@@ -677,7 +677,9 @@ extern "C" int plm_add_bias(float* x, const float* bias, int n_rows, int d, cuda
 // is the one head size of the cache and of the attention kernels, and what lies beyond a head's own width is
 // written as zero (a zero component adds nothing to a score; a zero value column is multiplied by zero weights of
 // the output projection).  One block per token; the token's q and k sit in shared memory between the sums of
-// squares and the rotation; sums in an order that depends on the sizes only.
+// squares and the rotation; sums in an order that depends on the sizes only.  A row of qkv is ld elements long (the
+// product may hold further columns, a gate's for instance, behind q, k and v); q_scale [H] (or null) multiplies head
+// h's queries after norm and rotation: a factor per head on its scores.
 __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 __device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
 
@@ -688,7 +690,8 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
                           Tc* __restrict__ vc, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                           const int* __restrict__ block_table, int max_pages, int H, int G, int D, int Dv, int hd_c,
-                          int rot_dim, int pairing, int own_kv, int per_head, int v_from_k) {
+                          int rot_dim, int pairing, int own_kv, int per_head, int v_from_k, long ld,
+                          const float* __restrict__ q_scale) {
     extern __shared__ float qk_sm[];                 // [nq + nk]
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -697,7 +700,7 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
     // v_from_k: there is no value projection; the keys as projected (with their bias, before norm and rotation) are the values
     const int nq = H * D, nk = own_kv ? G * D : 0, nv = own_kv && !v_from_k ? G * Dv : 0;
     const int pos = PLM_POSITION(tok_pos[t]);
-    const Ta* row = qkv + (size_t)t * (nq + nk + nv);
+    const Ta* row = qkv + (size_t)t * ld;           // (ld >= nq + nk + nv: the product may hold more columns behind them)
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < nq + nk; i += NT) {
         float v = to_f32<Ta>(row[i]);
@@ -741,6 +744,8 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
             for (int j = lane; j < D; j += 32) ss = fmaf(src[j], src[j], ss);
             r = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
         }
+        // a factor per query head on its scores: the query carries it (a rotation does not change it)
+        const float hs = is_q && q_scale ? q_scale[hh] : 1.0f;
         Tc* o;
         if (is_q) {
             o = q_out + ((size_t)t * H + hh) * hd_c;
@@ -764,6 +769,7 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
                 const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
                 a = ra; b = rb;
             }
+            a *= hs; b *= hs;
             if (ib == ia + 1) {
                 store_pair(o + ia, a, b);
             } else {
@@ -792,8 +798,10 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
                                       float eps, void* q_out, void* kc, void* vc, int out_dtype, const float* cos_t,
                                       const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
                                       int max_pages, int n_tokens, int H, int G, int D, int Dv, int hd_c, int rot_dim,
-                                      int pairing, int own_kv, int per_head, int v_from_k, cudaStream_t stream) {
+                                      int pairing, int own_kv, int per_head, int v_from_k, long ld, const float* q_scale,
+                                      cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
+    if (ld < (long)H * D + (own_kv ? (long)G * D + (v_from_k ? 0 : (long)G * Dv) : 0)) return PLM_ERR_SHAPE;
     if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || hd_c < D || hd_c < Dv || (hd_c & 1) || rot_dim < 0 || rot_dim > D ||
         (rot_dim & 1))
         return PLM_ERR_SHAPE;
@@ -807,7 +815,7 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
         return plm_status_of(launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
                                         (const Ta_*)qkv, bias, (const Tc_*)wq, (const Tc_*)wk, eps, (Tc_*)q_out, (Tc_*)kc, \
                                         (Tc_*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table, max_pages, H, G, D, Dv,  \
-                                        hd_c, rot_dim, pairing, own_kv, per_head, v_from_k));                          \
+                                        hd_c, rot_dim, pairing, own_kv, per_head, v_from_k, ld, q_scale));             \
     } while (0)
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_F32) QKN_LAUNCH(float, float);
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_BF16) QKN_LAUNCH(float, bf16);
@@ -942,5 +950,123 @@ extern "C" int plm_token_gate(const void* gate, int dtype, const void* table, in
     if (dtype == PLM_BF16 && table_dtype == PLM_BF16)
         return plm_status_of(launch_pdl(token_gate_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)gate,
                                         (const bf16*)table, ld_table, col0, tok, rows, (bf16*)out, n_rows, dim, vocab));
+    return PLM_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------------------ rotation in place
+// x [T, n_heads, hd] with row stride ld: the leading rot_dim components of every head are rotated by the row's position
+// (pairing 0: (x[i], x[i + rot_dim/2]); pairing 1: (x[2i], x[2i+1])), in fp32, in place; the others stay.  For rows that
+// reach attention by another way than a QKV product (queries taken into a latent's space, for instance).
+template <typename T>
+__global__ void rope_rows_kernel(T* __restrict__ x, long ld, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 const int* __restrict__ tok_pos, int n_rows, int n_heads, int hd, int rot_dim, int pairing) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int half = rot_dim / 2;
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)n_rows * n_heads * half) return;
+    const int j = (int)(i % half);
+    const long th = i / half;
+    const int head = (int)(th % n_heads), t = (int)(th / n_heads);
+    const int pos = PLM_POSITION(tok_pos[t]);
+    T* p = x + (long)t * ld + (long)head * hd;
+    const int ia = pairing == 0 ? j : 2 * j, ib = pairing == 0 ? j + half : 2 * j + 1;
+    const float a = to_f32<T>(p[ia]), b = to_f32<T>(p[ib]);
+    const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+    p[ia] = from_f32<T>(rope_first(a, b, c, s));
+    p[ib] = from_f32<T>(rope_second(a, b, c, s));
+}
+
+extern "C" int plm_rope_rows(void* x, int dtype, long ld, const float* cos_t, const float* sin_t, const int* tok_pos, int n_rows,
+                             int n_heads, int hd, int rot_dim, int pairing, cudaStream_t stream) {
+    if (n_rows <= 0 || rot_dim == 0) return PLM_OK;
+    if (n_heads <= 0 || hd <= 0 || rot_dim < 0 || (rot_dim & 1) || rot_dim > hd || ld < (long)n_heads * hd) return PLM_ERR_SHAPE;
+    if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)(((long)n_rows * n_heads * (rot_dim / 2) + 255) / 256));
+    if (dtype == PLM_F32)
+        return plm_status_of(launch_pdl(rope_rows_kernel<float>, grid, dim3(256), 0, stream, (float*)x, ld, cos_t, sin_t, tok_pos,
+                                        n_rows, n_heads, hd, rot_dim, pairing));
+    if (dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(rope_rows_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)x, ld, cos_t, sin_t, tok_pos,
+                                        n_rows, n_heads, hd, rot_dim, pairing));
+    return PLM_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------------------ two norms of one row
+// A layer whose mixer and feed-forward read the same x through norms of their own:
+//   out_a = x r w_a  (then, with `mix`, shifted towards the token before: out_a + (prev_a - out_a) * mix, where prev_a is
+//           the unshifted out_a of the sequence's token before, from `state` for a step's first token; zeros at position 0)
+//   out_b = x r w_b  (null: only out_a is made)
+// with r = 1 / sqrt(mean(x^2) + eps), all in fp32, w_a and w_b fp32 (a weight stored around zero arrives here as 1 + w).
+// One block per token; the block also works out the norm of the token before (its row of x is read once more, from the
+// L2 cache as a rule: the price of needing no second pass and no meeting between blocks), unless that token lies in
+// an earlier step.  `state` [slots][d] fp32 keeps each sequence's last unshifted out_a.  The sums run in an order that depends on d only, and the row before is normalised by
+// the same code as the row itself, so a position's result does not depend on how the prompt was cut.
+template <int NT>
+__device__ __forceinline__ float row_sum_squares(const float* __restrict__ row, int d) {
+    float ss = 0.f;
+    if ((d & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < d; i += NT * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += NT) ss += row[i] * row[i];
+    }
+    return ss;
+}
+
+template <typename To, int NT>
+__global__ void __launch_bounds__(NT)
+norm_pair_shift_kernel(const float* __restrict__ x, const float* __restrict__ w_a, const float* __restrict__ w_b,
+                       const float* __restrict__ mix, float* __restrict__ state, long state_stride,
+                       const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                       To* __restrict__ out_a, To* __restrict__ out_b, int d, float eps) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    // `other`: the row whose norm this block needs beside its own.  For a sequence's first token of the step that is the
+    // sequence's LAST token of the step, whose norm goes into the state: the block that reads the old state is the one
+    // that writes the new one, each thread its own elements, so that no block reads a state that is already new.
+    int first = 0, other = -1;
+    float* st = nullptr;
+    if (mix) {
+        const int b = PLM_SEQ_NO(tok_seq[t]);
+        first = t == seq_start[b];
+        other = first ? seq_start[b + 1] - 1 : t - 1;
+        if (other == t) other = -1;
+        st = state + (long)seq_slot[b] * state_stride;
+    }
+    const float* xr = x + (size_t)t * d;
+    const float* xo = x + (size_t)(other < 0 ? t : other) * d;
+    const float r = 1.0f / sqrtf(block_sum<NT>(row_sum_squares<NT>(xr, d), red) / (float)d + eps);
+    float ro = r;
+    if (other >= 0) ro = 1.0f / sqrtf(block_sum<NT>(row_sum_squares<NT>(xo, d), red) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += NT) {
+        const float v = xr[i];
+        const float a = v * r * w_a[i];
+        float o = a;
+        if (mix) {
+            const float prev = first ? st[i] : xo[i] * ro * w_a[i];
+            o = a + (prev - a) * mix[i];
+            if (first) st[i] = other < 0 ? a : xo[i] * ro * w_a[i];
+        }
+        out_a[(size_t)t * d + i] = from_f32<To>(o);
+        if (out_b) out_b[(size_t)t * d + i] = from_f32<To>(v * r * w_b[i]);
+    }
+}
+
+extern "C" int plm_norm_pair_shift(const float* x, const float* w_a, const float* w_b, const float* mix, float* state,
+                                   long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot, void* out_a,
+                                   void* out_b, int out_dtype, int n_tokens, int d, float eps, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (d <= 0 || (mix != nullptr && (state == nullptr || state_stride < d))) return PLM_ERR_SHAPE;
+    if (out_dtype == PLM_F32)
+        return plm_status_of(launch_pdl(norm_pair_shift_kernel<float, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
+                                        state, state_stride, tok_seq, seq_start, seq_slot, (float*)out_a, (float*)out_b, d, eps));
+    if (out_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(norm_pair_shift_kernel<bf16, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
+                                        state, state_stride, tok_seq, seq_start, seq_slot, (bf16*)out_a, (bf16*)out_b, d, eps));
     return PLM_ERR_DTYPE;
 }

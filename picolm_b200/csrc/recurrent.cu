@@ -702,16 +702,16 @@ extern "C" int plm_gated_norm(const void* x, int x_dtype, long ldx, const void* 
 }
 
 // ------------------------------------------------------------------------------------------------ one matrix per head
-// out[t, h, o] = sum_i W[h][o][i] * x[t, h, i], optionally times sigmoid(gate[t, h, o]).  x [T, H * I] with row stride
-// ldx, W [H, O, I], out [T, H * O].  Tiles of 64 tokens x 64 outputs, 4 x 4 of them a thread, the inputs walked 32 at
+// out[t, h, o] = sum_i W[h][o][i] * x[t, h, i], optionally times sigmoid(gate[t, h, o]) (gate_per_head: one gate a head,
+// sigmoid(gate[t, h])).  x [T, H * I] with row stride ldx, W [H, O, I], out [T, H * O].  Tiles of 64 tokens x 64 outputs, 4 x 4 of them a thread, the inputs walked 32 at
 // a time through shared memory, sums in fp32 in ascending order of i.
 #define HL_TT 64
 #define HL_TO 64
 #define HL_TI 32
-template <typename T>
+template <typename T, typename TG>
 __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ W,
-                                                          const T* __restrict__ gate, long ldg, T* __restrict__ out, long ldo,
-                                                          int n_tokens, int H, int O, int I) {
+                                                          const TG* __restrict__ gate, long ldg, T* __restrict__ out, long ldo,
+                                                          int n_tokens, int H, int O, int I, int gate_per_head) {
     __shared__ float xs[HL_TI][HL_TT + 4];                 // transposed: a thread reads its 4 tokens as one float4
     __shared__ float ws[HL_TI][HL_TO + 4];
     pdl_launch_dependents();
@@ -754,7 +754,7 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ 
             const int o = o0 + og * 4 + j;
             if (o >= O) continue;
             float val = acc[i][j];
-            if (gate) val *= sigmoid_f(to_f32<T>(gate[(long)t * ldg + (long)h * O + o]));
+            if (gate) val *= sigmoid_f(to_f32<TG>(gate[(long)t * ldg + (gate_per_head ? (long)h : (long)h * O + o)]));
             out[(long)t * ldo + (long)h * O + o] = from_f32<T>(val);
         }
     }
@@ -764,10 +764,10 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ 
 // row (h, o): it takes the row's I weights into registers (up to 32 a lane) and forms the dot product with every
 // token's x[t, h, :]; a lane's elements are I / 32 apart so that the warp's loads are contiguous.
 #define HLS_MAX_T 16
-template <typename T>
+template <typename T, typename TG>
 __global__ void __launch_bounds__(256) head_linear_small_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ W,
-                                                                const T* __restrict__ gate, long ldg, T* __restrict__ out,
-                                                                long ldo, int n_tokens, int H, int O, int I) {
+                                                                const TG* __restrict__ gate, long ldg, T* __restrict__ out,
+                                                                long ldo, int n_tokens, int H, int O, int I, int gate_per_head) {
     pdl_launch_dependents();
     const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;          // h * O + o
     const int lane = threadIdx.x & 31;
@@ -791,39 +791,38 @@ __global__ void __launch_bounds__(256) head_linear_small_kernel(const T* __restr
         }
         acc = warp_sum(acc);
         if (lane == 0) {
-            if (gate) acc *= sigmoid_f(to_f32<T>(gate[(long)t * ldg + row]));
+            if (gate) acc *= sigmoid_f(to_f32<TG>(gate[(long)t * ldg + (gate_per_head ? (long)h : row)]));
             out[(long)t * ldo + row] = from_f32<T>(acc);
         }
     }
 }
 
-extern "C" int plm_head_linear(const void* x, int dtype, long ldx, const void* W, const void* gate, long ldg, void* out, long ldo,
-                               int n_tokens, int H, int O, int I, cudaStream_t stream) {
-    if (n_tokens <= 0 || H <= 0 || O <= 0 || I <= 0 || H > 65535) return PLM_ERR_SHAPE;
-    cudaError_t e;
+template <typename T, typename TG>
+static int head_linear_launch(const void* x, long ldx, const void* W, const void* gate, long ldg, void* out, long ldo, int n_tokens,
+                              int H, int O, int I, int gate_per_head, cudaStream_t stream) {
     if (n_tokens <= HLS_MAX_T && I <= 1024) {
         const unsigned blocks = (unsigned)(((long)H * O * 32 + 255) / 256);
-        if (dtype == PLM_F32)
-            e = launch_pdl(head_linear_small_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, ldx, (const float*)W,
-                           (const float*)gate, ldg, (float*)out, ldo, n_tokens, H, O, I);
-        else if (dtype == PLM_BF16)
-            e = launch_pdl(head_linear_small_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W,
-                           (const bf16*)gate, ldg, (bf16*)out, ldo, n_tokens, H, O, I);
-        else
-            return PLM_ERR_DTYPE;
-        return plm_status_of(e);
+        return plm_status_of(launch_pdl(head_linear_small_kernel<T, TG>, dim3(blocks), dim3(256), 0, stream, (const T*)x, ldx,
+                                        (const T*)W, (const TG*)gate, ldg, (T*)out, ldo, n_tokens, H, O, I, gate_per_head));
     }
     const dim3 grid((O + HL_TO - 1) / HL_TO, (n_tokens + HL_TT - 1) / HL_TT, H);
     if (grid.y > 65535) return PLM_ERR_SHAPE;
-    if (dtype == PLM_F32)
-        e = launch_pdl(head_linear_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ldx, (const float*)W, (const float*)gate,
-                       ldg, (float*)out, ldo, n_tokens, H, O, I);
-    else if (dtype == PLM_BF16)
-        e = launch_pdl(head_linear_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W, (const bf16*)gate,
-                       ldg, (bf16*)out, ldo, n_tokens, H, O, I);
-    else
-        return PLM_ERR_DTYPE;
-    return plm_status_of(e);
+    return plm_status_of(launch_pdl(head_linear_kernel<T, TG>, grid, dim3(256), 0, stream, (const T*)x, ldx, (const T*)W,
+                                    (const TG*)gate, ldg, (T*)out, ldo, n_tokens, H, O, I, gate_per_head));
+}
+
+// dtype: x, W and out; gate_dtype: the gate (that type or PLM_F32)
+extern "C" int plm_head_linear(const void* x, int dtype, long ldx, const void* W, const void* gate, int gate_dtype, long ldg,
+                               void* out, long ldo, int n_tokens, int H, int O, int I, int gate_per_head, cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0 || O <= 0 || I <= 0 || H > 65535) return PLM_ERR_SHAPE;
+    if (gate == nullptr) gate_dtype = dtype;
+    if (dtype == PLM_F32 && gate_dtype == PLM_F32)
+        return head_linear_launch<float, float>(x, ldx, W, gate, ldg, out, ldo, n_tokens, H, O, I, gate_per_head, stream);
+    if (dtype == PLM_BF16 && gate_dtype == PLM_BF16)
+        return head_linear_launch<bf16, bf16>(x, ldx, W, gate, ldg, out, ldo, n_tokens, H, O, I, gate_per_head, stream);
+    if (dtype == PLM_BF16 && gate_dtype == PLM_F32)
+        return head_linear_launch<bf16, float>(x, ldx, W, gate, ldg, out, ldo, n_tokens, H, O, I, gate_per_head, stream);
+    return PLM_ERR_DTYPE;
 }
 
 // ------------------------------------------------------------------------------------------------ rows into pages
@@ -856,6 +855,63 @@ extern "C" int plm_store_rows_paged(const void* rows, int dtype, long ld, void* 
     else
         return PLM_ERR_DTYPE;
     return plm_status_of(e);
+}
+
+// A latent's row as the cache keeps it, made from the projection's columns in one pass: rows [T, n_rot + n_norm] with row
+// stride ld hold `n_rot` columns that are rotated by the token's position (half-split or neighbouring pairs; a key part
+// that all heads share) and then `n_norm` columns that are divided by their root mean square (eps inside the root) and
+// multiplied by w [n_norm] (fp32); the page's row is [rotated | normed | zeros] of width R >= n_rot + n_norm.  Everything
+// in fp32; one warp per token, the sum of squares in an order that depends on n_norm only.
+template <typename Ti, typename To>
+__global__ void __launch_bounds__(128)
+latent_store_kernel(const Ti* __restrict__ rows, long ld, const float* __restrict__ w, float eps, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, To* __restrict__ pages, const int* __restrict__ tok_pos,
+                    const int* __restrict__ tok_seq, const int* __restrict__ block_table, int pages_per_seq, int n_tokens,
+                    int n_rot, int n_norm, int R, int pairing) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n_tokens) return;
+    const int pos = PLM_POSITION(tok_pos[t]);
+    const int page = PLM_PAGE_NO(block_table[(long)PLM_SEQ_NO(tok_seq[t]) * pages_per_seq + pos / PLM_PAGE]);
+    const Ti* src = rows + (long)t * ld;
+    To* dst = pages + ((long)page * PLM_PAGE + pos % PLM_PAGE) * R;
+    float ss = 0.f;
+    for (int j = lane; j < n_norm; j += 32) {
+        const float v = to_f32<Ti>(src[n_rot + j]);
+        ss = fmaf(v, v, ss);
+    }
+    const float r = 1.0f / sqrtf(warp_sum(ss) / (float)n_norm + eps);
+    const int half = n_rot / 2;
+    for (int j = lane; j < half; j += 32) {
+        const int ia = pairing == 0 ? j : 2 * j, ib = pairing == 0 ? j + half : 2 * j + 1;
+        const float a = to_f32<Ti>(src[ia]), b = to_f32<Ti>(src[ib]);
+        const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+        dst[ia] = from_f32<To>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+        dst[ib] = from_f32<To>(__fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)));
+    }
+    for (int j = lane; j < n_norm; j += 32) dst[n_rot + j] = from_f32<To>(to_f32<Ti>(src[n_rot + j]) * r * w[j]);
+    for (int j = n_rot + n_norm + lane; j < R; j += 32) dst[j] = from_f32<To>(0.f);
+}
+
+extern "C" int plm_latent_store(const void* rows, int in_dtype, long ld, const float* w, float eps, const float* cos_t,
+                                const float* sin_t, void* pages, int out_dtype, const int* tok_pos, const int* tok_seq,
+                                const int* block_table, int pages_per_seq, int n_tokens, int n_rot, int n_norm, int R,
+                                int pairing, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (n_rot < 0 || (n_rot & 1) || n_norm <= 0 || R < n_rot + n_norm || ld < n_rot + n_norm || (n_rot > 0 && cos_t == nullptr))
+        return PLM_ERR_SHAPE;
+    if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)((n_tokens + 3) / 4));
+#define LS_LAUNCH(Ti_, To_)                                                                                                     \
+    return plm_status_of(launch_pdl(latent_store_kernel<Ti_, To_>, grid, dim3(128), 0, stream, (const Ti_*)rows, ld, w, eps, cos_t, \
+                                    sin_t, (To_*)pages, tok_pos, tok_seq, block_table, pages_per_seq, n_tokens, n_rot, n_norm, R, \
+                                    pairing))
+    if (in_dtype == PLM_F32 && out_dtype == PLM_F32) LS_LAUNCH(float, float);
+    if (in_dtype == PLM_F32 && out_dtype == PLM_BF16) LS_LAUNCH(float, bf16);
+    if (in_dtype == PLM_BF16 && out_dtype == PLM_BF16) LS_LAUNCH(bf16, bf16);
+#undef LS_LAUNCH
+    return PLM_ERR_DTYPE;
 }
 
 // ------------------------------------------------------------------------------------------------ gated diagonal recurrence

@@ -1,11 +1,14 @@
 // A routed feed-forward (mixture of experts): the router's choice, the sort of the chosen (token, expert) pairs by
 // expert, the experts' two products over those pairs, and the weighted sum per token.
 //
-//   scores   s_e = sigmoid(z_e) from the router's logits z (fp32); the choice is made on c_e = s_e + correction_e
+//   scores   s_e = sigmoid(z_e), or softmax(z)_e over all router outputs, from the router's logits z (fp32); the choice is
+//            made on c_e = s_e + correction_e
 //   groups   the experts form n_groups equal groups of neighbours; a group's score is the sum of its two largest
-//            c_e; only experts of the `keep` best groups can be chosen (the others count as -inf)
+//            c_e, or its largest; only experts of the `keep` best groups can be chosen (the others count as -inf)
 //   choice   the `top` largest c_e (the lower index on ties)
-//   weights  w = s_chosen / (sum of the chosen s + 1e-20) * scale     (s without the correction)
+//   weights  w = s_chosen / (sum of the chosen s + 1e-20) * scale, or s_chosen * scale   (s without the correction)
+//   identity the router's last outputs may be experts without tensors whose output is their input: they take part in
+//            scores, groups and choice like the others, are left out of the sort, and enter the weighted sum as w * h
 //   expert   y = W_down (silu(W_gate h) * (W_up h)), no biases
 //   output   out[t] = sum_k w[t, k] y_(e[t, k])(h[t])  (+ gate[t] * shared[t] for an expert every token uses)
 //
@@ -28,7 +31,7 @@ constexpr int ROUTE_WARPS = 4;
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction, int E, int top,
                   int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
-                  float* __restrict__ gate, int gate_col, int T) {
+                  float* __restrict__ gate, int gate_col, int T, int softmax_scores, int group_by_max, int normalize) {
     extern __shared__ float route_sm[];             // per warp: s[E], c[E], group score[n_groups], group kept[n_groups]
     pdl_launch_dependents();
     pdl_wait();
@@ -40,8 +43,19 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
     float* gs = c + E;
     float* kept = gs + n_groups;
     const float* z = logits + (size_t)t * ld;
+    float zmax = 0.f, zden = 1.f;
+    if (softmax_scores) {
+        // softmax over all E outputs: the maximum, then the sum of the exponentials, each in an order E alone fixes
+        zmax = -INFINITY;
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+        float part = 0.f;
+        for (int e = lane; e < E; e += 32) part += expf(z[e] - zmax);
+        zden = warp_sum(part);
+    }
     for (int e = lane; e < E; e += 32) {
-        const float v = 1.0f / (1.0f + expf(-z[e]));
+        const float v = softmax_scores ? expf(z[e] - zmax) / zden : 1.0f / (1.0f + expf(-z[e]));
         float cv = v + (correction ? correction[e] : 0.f);
         if (!(cv == cv)) cv = -INFINITY;            // a NaN is never chosen before anything else
         s[e] = v;
@@ -56,7 +70,7 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
                 const float v = c[g * per + j];
                 if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
             }
-            gs[g] = per >= 2 ? a + b : a;
+            gs[g] = per >= 2 && !group_by_max ? a + b : a;
             kept[g] = 0.f;
         }
         __syncwarp();
@@ -109,7 +123,10 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
     }
     if (lane == 0) {
         const float den = sum + 1e-20f;
-        for (int r = 0; r < top; ++r) weights[(size_t)t * top + r] = weights[(size_t)t * top + r] / den * scale;
+        for (int r = 0; r < top; ++r) {
+            const float wv = weights[(size_t)t * top + r];
+            weights[(size_t)t * top + r] = normalize ? wv / den * scale : wv * scale;
+        }
         if (gate) gate[t] = 1.0f / (1.0f + expf(-z[gate_col]));
     }
 }
@@ -177,11 +194,12 @@ router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* 
 // ---------------------------------------------------------------------- the sort
 // One block.  ids [n_entries] -> sorted [max_tiles * BM] (entry or -1), tile_expert [max_tiles] (expert or -1),
 // where [n_entries] the row of `sorted` that holds the entry.  Where an entry lands inside its expert's rows depends on
-// the order of the atomics; no result depends on it.
+// the order of the atomics; no result depends on it.  Entries whose id lies in [E, E + n_skip) (experts without
+// tensors) are left out: where = -1.
 constexpr int ALIGN_NT = 1024;
 __global__ void __launch_bounds__(ALIGN_NT)
 moe_align_kernel(const int* __restrict__ ids, int n_entries, int E, int BM, int* __restrict__ tile_expert,
-                 int* __restrict__ sorted, int* __restrict__ where, int max_tiles) {
+                 int* __restrict__ sorted, int* __restrict__ where, int max_tiles, int n_skip) {
     extern __shared__ int align_sm[];               // cnt[E], off[E + 1], fill[E]
     pdl_launch_dependents();
     pdl_wait();
@@ -192,6 +210,7 @@ moe_align_kernel(const int* __restrict__ ids, int n_entries, int E, int BM, int*
     __syncthreads();
     for (int i = threadIdx.x; i < n_entries; i += ALIGN_NT) {
         int e = ids[i];
+        if (e >= E && e < E + n_skip) continue;
         if (e < 0 || e >= E) e = 0;
         atomicAdd(&cnt[e], 1);
     }
@@ -222,6 +241,7 @@ moe_align_kernel(const int* __restrict__ ids, int n_entries, int E, int BM, int*
     __syncthreads();
     for (int i = threadIdx.x; i < n_entries; i += ALIGN_NT) {
         int e = ids[i];
+        if (e >= E && e < E + n_skip) { where[i] = -1; continue; }
         if (e < 0 || e >= E) e = 0;
         const int p = off[e] + atomicAdd(&fill[e], 1);
         if (p < max_tiles * BM) sorted[p] = i;
@@ -460,14 +480,21 @@ __global__ void moe_gather_kernel(const uint8_t* __restrict__ src, uint8_t* __re
 }
 
 // ------------------------------------------------------------------- the weighted sum
-// out[t, :] = sum_k weights[t, k] * y[where[t * top + k], :]  (+ gate[t] * shared[t, :]), k ascending, fp32.
+// sum[t, :] = sum_k weights[t, k] * (where[t * top + k] >= 0 ? y[where[t * top + k], :] : ident[t, :])  (+ gate[t] * shared[t, :])
+// with k ascending, fp32: a pair that the sort left out (where < 0) belongs to an expert whose output is its input,
+// `ident` [T, d] in Th.  Then out[t, :] = (accumulate ? out[t, :] : 0) + out_scale * (sum[t, :] + add[t, :]): `add` (fp32
+// [T, d] or null) is what a sublayer beside the feed-forward made of the same x, and with `accumulate` the result goes
+// straight into the residual stream.
+template <typename Th>
 __global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const int* __restrict__ where,
                                    const float* __restrict__ weights, int top, const float* __restrict__ shared,
-                                   const float* __restrict__ gate, float* __restrict__ out, int d) {
+                                   const float* __restrict__ gate, float* __restrict__ out, int d,
+                                   const Th* __restrict__ ident, const float* __restrict__ add, float out_scale, int accumulate) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    if (d % 4 == 0 && ldy % 4 == 0 && ((((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15) == 0)) {
+    const bool plain = ident == nullptr && add == nullptr && out_scale == 1.0f && !accumulate;
+    if (plain && d % 4 == 0 && ldy % 4 == 0 && ((((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15) == 0)) {
         // four columns a thread (the same sums in the same order)
         for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -487,9 +514,15 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const 
     }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k)
-            acc = fmaf(weights[(size_t)t * top + k], y[(size_t)where[(size_t)t * top + k] * ldy + i], acc);
+        for (int k = 0; k < top; ++k) {
+            const int row = where[(size_t)t * top + k];
+            const float v = row >= 0 ? y[(size_t)row * ldy + i] : (ident ? to_f32<Th>(ident[(size_t)t * d + i]) : 0.f);
+            acc = fmaf(weights[(size_t)t * top + k], v, acc);
+        }
         if (shared) acc = fmaf(gate ? gate[t] : 1.0f, shared[(size_t)t * d + i], acc);
+        if (add) acc += add[(size_t)t * d + i];
+        acc *= out_scale;
+        if (accumulate) acc += out[(size_t)t * d + i];
         out[(size_t)t * d + i] = acc;
     }
 }
@@ -521,7 +554,7 @@ extern "C" int plm_router_logits(const void* h, int h_dtype, const void* w, int 
 
 extern "C" int plm_route_topk(const float* logits, int ld, const float* correction, int E, int top, int n_groups,
                               int keep, float scale, int* ids, float* weights, float* gate, int gate_col, int n_tokens,
-                              cudaStream_t stream) {
+                              int softmax_scores, int group_by_max, int normalize, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (E <= 0 || top <= 0 || top > E || n_groups <= 0 || E % n_groups || keep <= 0 || keep > n_groups || ld < E)
         return PLM_ERR_SHAPE;
@@ -531,7 +564,7 @@ extern "C" int plm_route_topk(const float* logits, int ld, const float* correcti
     if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return plm_status_of(launch_pdl(route_topk_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
                                     smem, stream, logits, ld, correction, E, top, n_groups, keep, scale, ids, weights, gate,
-                                    gate_col, n_tokens));
+                                    gate_col, n_tokens, softmax_scores, group_by_max, normalize));
 }
 
 // The most tiles of `bm` rows that `n_entries` pairs over `n_experts` experts can fill: every tile holds at least
@@ -542,14 +575,14 @@ extern "C" int plm_moe_max_tiles(int n_entries, int n_experts, int bm) {
 }
 
 extern "C" int plm_moe_align(const int* ids, int n_entries, int E, int bm, int* tile_expert, int* sorted, int* where,
-                             int max_tiles, cudaStream_t stream) {
+                             int max_tiles, int n_skip, cudaStream_t stream) {
     if (n_entries <= 0) return PLM_OK;
     if (E <= 0 || bm <= 0 || max_tiles <= 0) return PLM_ERR_SHAPE;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 200 * 1024) return PLM_ERR_SHAPE;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return plm_status_of(launch_pdl(moe_align_kernel, dim3(1), dim3(ALIGN_NT), smem, stream, ids, n_entries, E, bm, tile_expert,
-                                    sorted, where, max_tiles));
+                                    sorted, where, max_tiles, n_skip));
 }
 
 // mode 0: gate/up with SiLU (a [T, K], out [max_tiles * bm, N] of a's type); mode 1: down (a [max_tiles * bm, K] of
@@ -601,9 +634,14 @@ extern "C" int plm_moe_gather(const void* src, void* dst, const int* sorted, int
 }
 
 extern "C" int plm_moe_combine(const float* y, long ldy, const int* where, const float* weights, int top,
-                               const float* shared, const float* gate, float* out, int n_tokens, int d, cudaStream_t stream) {
+                               const float* shared, const float* gate, float* out, int n_tokens, int d, const void* ident,
+                               int ident_dtype, const float* add, float out_scale, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (d <= 0 || top <= 0) return PLM_ERR_SHAPE;
-    return plm_status_of(launch_pdl(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, y, ldy, where, weights, top,
-                                    shared, gate, out, d));
+    if (ident != nullptr && ident_dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, y, ldy, where, weights, top,
+                                        shared, gate, out, d, (const bf16*)ident, add, out_scale, accumulate));
+    if (ident != nullptr && ident_dtype != PLM_F32) return PLM_ERR_DTYPE;
+    return plm_status_of(launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, y, ldy, where, weights, top,
+                                    shared, gate, out, d, (const float*)ident, add, out_scale, accumulate));
 }

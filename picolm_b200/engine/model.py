@@ -105,24 +105,34 @@ class Model:
     def cache_specs(self) -> List[CacheSpec]:
         """What the runs of the schedule own in the cache, as one flat list: for every run that owns
         its caches, what its arrangement asks for (one entry per part that keeps something; none for a
-        layer without such parts).  The position in this list is the cache's number in `SequenceCache`."""
+        layer without such parts).  The position in this list is the cache's number in `SequenceCache`.
+        A run of a layer with `cache_of` reads the lending layer's caches in their order, except those marked
+        `private` on either side: the lender's private caches are passed over, the borrower's are its own."""
         out: List[CacheSpec] = []
-        self._run_caches: List[Tuple[List[int], bool]] = []       # per run: (cache numbers, may write them)
+        self._run_caches: List[List[Tuple[int, bool]]] = []       # per run: (cache number, may write it) per entry
         for run, i in enumerate(self.spec.schedule):
             layer = self.spec.layers[i]
+            specs = list(self.blocks[i].cache_specs())
             if layer.cache_of is None:
-                specs = list(self.blocks[i].cache_specs())
-                self._run_caches.append((list(range(len(out), len(out) + len(specs))), True))
+                self._run_caches.append([(len(out) + n, True) for n in range(len(specs))])
                 out.extend(specs)
                 continue
             src = next((r for r in range(run - 1, -1, -1) if self.spec.schedule[r] == layer.cache_of), None)
             if src is None:
                 raise ValueError(f"run {run}: layer {layer.cache_of}, whose cache it reads, has not run before it")
-            ids = self._run_caches[src][0]
-            if len(ids) != len(self.blocks[i].cache_specs()):
-                raise ValueError(f"layer {i} reads the caches of layer {layer.cache_of}, which keeps {len(ids)}; "
-                                 f"its own parts want {len(self.blocks[i].cache_specs())}")
-            self._run_caches.append((ids, False))
+            lent = [c for (c, _), sp in zip(self._run_caches[src], self.blocks[layer.cache_of].cache_specs()) if not sp.private]
+            wanted = [sp for sp in specs if not sp.private]
+            if len(lent) != len(wanted):
+                raise ValueError(f"layer {i} reads the caches of layer {layer.cache_of}, which lends {len(lent)}; "
+                                 f"its own parts want {len(wanted)}")
+            entries, lent = [], list(lent)
+            for sp in specs:
+                if sp.private:
+                    entries.append((len(out), True))
+                    out.append(sp)
+                else:
+                    entries.append((lent.pop(0), False))
+            self._run_caches.append(entries)
         return out
 
     def prepare(self, max_seq_tokens: int) -> None:
@@ -132,9 +142,8 @@ class Model:
     def layer_caches(self, run: int, cache: SequenceCache, step) -> list:
         """What the parts of a run see of the cache: one `KVLayerCache` or `StateLayerCache` per entry of
         the arrangement's `cache_specs()`, in that order."""
-        ids, writable = self._run_caches[run]
         out = []
-        for c in ids:
+        for c, writable in self._run_caches[run]:
             if c in cache.layer_group:
                 gi = cache.layer_group[c]
                 g = cache.kv_groups[gi]

@@ -11,13 +11,13 @@ from .attention import (DECODE_CLUSTER_SPLITS, Rotation, attention, attention_de
 from .chain import Chain, LazyRows  # noqa: F401
 from .elementwise import (GATE_ACTIVATIONS, add_bias, add_rows, dyt_norm, embed, gather_rows, layernorm,  # noqa: F401
                           post_pre_norm, post_pre_norm_supported, qk_norm_rope_store, rmsnorm, rope_store, scaled_sum,
-                          swiglu, token_gate)
+                          swiglu, token_gate, rope_rows, norm_pair_shift)
 from .gemm import (PendingLinear, ScaledRows, gemm_simt, gemm_tc_skinny, gemm_tc_supported,  # noqa: F401
                    gemm_tc_wide, interleave_gate_up, linear, linear_residual_norm, linear_swiglu, pair_pays,
                    residual_norm_supported)
 from .recurrent import (DECAY_SIGMOID, DECAY_STEP, GATE_AFTER_NORM, GATE_BEFORE_NORM, GATE_NONE, causal_conv,  # noqa: F401
                         delta_prep, delta_scan, diag_scan, gated_norm, head_linear, linear_scan, rglru_gates,
-                        store_rows_paged)
+                        store_rows_paged, latent_store)
 from .routed import (SortedPairs, moe_align, moe_combine, moe_down, moe_down_tc, moe_gate_up, moe_gate_up_tc,  # noqa: F401
                      moe_gather, moe_max_tiles, moe_tc_supported, route_topk, router_logits)
 from .sampling import argmax, sample  # noqa: F401

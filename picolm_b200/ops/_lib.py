@@ -24,20 +24,23 @@ _SIGNATURES = {
     "plm_layernorm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_add_bias": [_vp, _vp, _i, _i, _vp],
     "plm_qk_norm_rope_store": [_vp, _i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                               _i, _i, _i, _i, _i, _i, _vp],
+                               _i, _i, _i, _i, _i, _i, _l, _vp, _vp],
+    "plm_rope_rows": [_vp, _i, _l, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "plm_norm_pair_shift": [_vp, _vp, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "plm_latent_store": [_vp, _i, _l, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "plm_dyt_norm": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp],
     "plm_add_rows": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "plm_scaled_sum": [_vp, _f, _vp, _vp, _f, _vp, _i, _i, _vp],
     "plm_token_gate": [_vp, _i, _vp, _i, _l, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "plm_route_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
+    "plm_route_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_moe_max_tiles": [_i, _i, _i],
     "plm_gate_constants": [_f, _f],
     "plm_router_logits": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _vp],
-    "plm_moe_align": [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "plm_moe_align": [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
     "plm_moe_gemm": [_vp, _l, _i, _vp, _vp, _l, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_wide_grouped": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _i, _vp, _vp, _vp],
     "plm_moe_gather": [_vp, _vp, _vp, _i, _i, _l, _vp],
-    "plm_moe_combine": [_vp, _l, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
+    "plm_moe_combine": [_vp, _l, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _f, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],
@@ -75,7 +78,7 @@ _SIGNATURES = {
     "plm_sigmoid_decay": [_vp, _i, _l, _vp, _f, _vp, _i, _i, _vp],
     "plm_linear_scan_plan": [_i, _i, _i, _i, _i, _i, _vp],
     "plm_gated_norm": [_vp, _i, _l, _vp, _i, _l, _vp, _i, _vp, _i, _l, _i, _i, _i, _f, _i, _i, _i, _vp],
-    "plm_head_linear": [_vp, _i, _l, _vp, _vp, _l, _vp, _l, _i, _i, _i, _i, _vp],
+    "plm_head_linear": [_vp, _i, _l, _vp, _vp, _i, _l, _vp, _l, _i, _i, _i, _i, _i, _vp],
     "plm_store_rows_paged": [_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],

@@ -206,7 +206,8 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
                        k_norm: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, kv, rotation, step,
                        num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, own_kv: bool = True,
-                       per_head: bool = False, values_from_keys: bool = False) -> None:
+                       per_head: bool = False, values_from_keys: bool = False,
+                       q_scale: Optional[torch.Tensor] = None) -> None:
     """What stands between a QKV product and attention where queries and keys are normalised over all their heads at
     once: per token, in fp32, `q + bias` and `k + bias` are divided by their root mean square over ALL their columns
     and multiplied by `q_norm` / `k_norm` (None: no norm), the leading `rotation.rotary_dim` components of every head
@@ -215,8 +216,12 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
     head size hd_c >= D, Dv: what lies beyond a head's own width is written as zero).  `rotation`: `ops.Rotation` or
     None.  `per_head`: the root mean square is taken over each head's own D columns, and `q_norm` / `k_norm` are [D],
     serving every head.  `values_from_keys`: qkv holds no values; `k + bias` as projected, before norm and rotation,
-    is written as the value (Dv = D)."""
-    _dev(qkv, "qkv"), _dev(q_out, "q_out")
+    is written as the value (Dv = D).  `qkv` may be the leading columns of a wider matrix (a slice with contiguous
+    rows).  `q_scale` (float32 [H]): head h's queries times q_scale[h] after norm and rotation, a factor per head on
+    its scores."""
+    if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("qk_norm_rope_store: qkv must be a matrix with contiguous rows on the device")
+    _dev(q_out, "q_out")
     _i32(step.tok_pos, "tok_pos"), _i32(step.tok_seq, "tok_seq"), _i32(kv.block_table, "block_table")
     T = qkv.shape[0]
     H, G, D, Dv = num_heads, num_kv_heads, key_dim, value_dim
@@ -233,6 +238,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
                 raise KernelError(f"qk_norm_rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd_c}] of {q_out.dtype}")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape != (cols,) or not bias.is_cuda):
         raise KernelError("qk_norm_rope_store: bias must be float32, one per column of qkv")
+    _f32_vec(q_scale, "q_scale", H)
     for wn, n, size in ((q_norm, "q_norm", D if per_head else H * D), (k_norm if own_kv else None, "k_norm", D if per_head else G * D)):
         if wn is not None and (wn.dtype != q_out.dtype or wn.shape != (size,) or not wn.is_cuda):
             raise KernelError(f"qk_norm_rope_store: {n} must be [{size}] of {q_out.dtype}")
@@ -250,7 +256,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
         _p(qkv), _dt(qkv, "qkv"), _p(bias), _p(q_norm), _p(k_norm) if own_kv else None, float(eps), _p(q_out),
         _p(kv.k) if own_kv else None, _p(kv.v) if own_kv else None, _dt(q_out, "q_out"), _p(cos), _p(sin),
         _p(step.tok_pos), _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, D, Dv, hd_c, rot,
-        0 if pairing == "half" else 1, 1 if own_kv else 0, 1 if per_head else 0, 1 if values_from_keys else 0, _stream()),
+        0 if pairing == "half" else 1, 1 if own_kv else 0, 1 if per_head else 0, 1 if values_from_keys else 0,
+        qkv.stride(0), _p(q_scale), _stream()),
         f"qk_norm_rope_store T={T}",
         nbytes=qkv.numel() * qkv.element_size() + T * (H + (2 * G if own_kv else 0)) * hd_c * q_out.element_size())
 
@@ -358,3 +365,55 @@ def token_gate(gate: torch.Tensor, table: torch.Tensor, first_column: int, token
         _p(gate), _dt(gate, "gate"), _p(table), _dt(table, "table"), table.shape[1], int(first_column), _p(tokens), _p(rows),
         _p(out), R, dim, table.shape[0], _stream()), f"token_gate rows={R} dim={dim}", nbytes=3 * R * dim * gate.element_size())
     return out
+
+
+def rope_rows(x: torch.Tensor, rotation, tok_pos: torch.Tensor, n_heads: int, head_dim: int) -> torch.Tensor:
+    """The leading `rotation.rotary_dim` components of every head of `x` [T, n_heads * head_dim] (contiguous rows; a
+    column slice will do) rotated in place by the rows' positions `tok_pos`; returns x.  For rows that reach
+    attention by another way than a QKV product."""
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != n_heads * head_dim:
+        raise KernelError(f"rope_rows: x must be [T, {n_heads * head_dim}] with contiguous rows on the device")
+    _i32(tok_pos, "tok_pos")
+    if rotation is None or rotation.cos is None or rotation.rotary_dim == 0:
+        return x
+    cos, sin, rot = rotation.cos, rotation.sin, rotation.rotary_dim
+    if cos.dtype != torch.float32 or cos.shape[1] != rot // 2 or sin.shape != cos.shape or rot > head_dim:
+        raise KernelError("rope_rows: cos/sin tables must be float32 [positions, rotary_dim/2], rotary_dim at most head_dim")
+    set_bounds("elementwise", n_positions=cos.shape[0], device=x.device)
+    _check(_fn("elementwise", "plm_rope_rows")(_p(x), _dt(x, "x"), x.stride(0), _p(cos), _p(sin), _p(tok_pos), x.shape[0],
+                                               int(n_heads), int(head_dim), int(rot), 0 if rotation.pairing == "half" else 1,
+                                               _stream()), f"rope_rows T={x.shape[0]} heads={n_heads}",
+           nbytes=2 * x.shape[0] * n_heads * rot * x.element_size())
+    return x
+
+
+def norm_pair_shift(x: torch.Tensor, w_a: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                    w_b: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                    state: Optional[torch.Tensor] = None, step=None):
+    """Two RMS norms of the same rows of the fp32 stream `x` [T, d] in one pass: `a = x r w_a`, `b = x r w_b` with
+    `r = 1 / sqrt(mean(x^2) + eps)` (w_a, w_b float32 [d]; without w_b only a is made).  With `mix` (float32 [d]) a is
+    shifted towards the sequence's token before: `a_t + (a_(t-1) - a_t) * mix`, a_(t-1) unshifted; for a step's first
+    token it comes from `state` (float32 [slots + 1, >= d], contiguous rows; zeros at a sequence's start), which is
+    brought up to date.  Returns (a, b) in `out_dtype` (b None without w_b)."""
+    _dev(x, "x")
+    if x.dtype != torch.float32 or x.dim() != 2:
+        raise KernelError("the residual stream must be float32 [T, d]")
+    T, d = x.shape
+    _f32_vec(w_a, "w_a", d), _f32_vec(w_b, "w_b", d), _f32_vec(mix, "mix", d)
+    if w_a is None:
+        raise KernelError("norm_pair_shift: w_a is needed")
+    lds = 0
+    if mix is not None:
+        if state is None or step is None or not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 \
+                or state.stride(1) != 1 or state.shape[1] < d:
+            raise KernelError("norm_pair_shift: a shift needs the step and a float32 state [slots, >= d] on the device")
+        lds = state.stride(0)
+        set_bounds("elementwise", n_seqs=step.n_seqs, device=x.device)
+    out_a = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    out_b = torch.empty((T, d), dtype=out_dtype, device=x.device) if w_b is not None else None
+    _check(_fn("elementwise", "plm_norm_pair_shift")(
+        _p(x), _p(w_a), _p(w_b), _p(mix), _p(state) if mix is not None else None, lds,
+        _p(step.tok_seq) if mix is not None else None, _p(step.seq_start) if mix is not None else None,
+        _p(step.seq_slot) if mix is not None else None, _p(out_a), _p(out_b), _dt(out_a, "out"), T, d, float(eps), _stream()),
+        f"norm_pair_shift rows={T} d={d}", nbytes=T * d * (4 + (2 if w_b is not None else 1) * out_a.element_size()))
+    return out_a, out_b

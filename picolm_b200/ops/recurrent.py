@@ -182,9 +182,11 @@ def gated_norm(x: torch.Tensor, out_dtype: torch.dtype, weight: Optional[torch.T
     return out
 
 
-def head_linear(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+def head_linear(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                gate_per_head: bool = False) -> torch.Tensor:
     """out[t, h, :] = weight[h] @ x[t, h, :] for `weight` [H, O, I] and `x` [T, H * I] (a column slice will do), with
-    float32 sums; optionally times sigmoid(gate) for `gate` [T, H * O].  Returns [T, H * O] of x's type."""
+    float32 sums; optionally times sigmoid(gate) for `gate` [T, H * O], or with `gate_per_head` [T, H]: one gate for
+    all of a head's outputs.  Returns [T, H * O] of x's type."""
     ldx = _cols(x, "x")
     _dev(weight, "weight")
     H, O, I = weight.shape
@@ -194,11 +196,12 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tens
     ldg = 0
     if gate is not None:
         ldg = _cols(gate, "gate")
-        if gate.shape != (T, H * O) or gate.dtype != x.dtype:
-            raise KernelError("head_linear: the gate must be [T, H * O] of x's type")
+        if gate.shape != (T, H if gate_per_head else H * O) or gate.dtype not in (x.dtype, torch.float32):
+            raise KernelError("head_linear: the gate must be [T, H * O] (per head: [T, H]) of x's type or float32")
     out = torch.empty((T, H * O), dtype=x.dtype, device=x.device)
     _check(_fn("recurrent", "plm_head_linear")(
-        _p(x), _dt(x, "x"), ldx, _p(weight), _p(gate), ldg, _p(out), H * O, T, H, O, I, _stream()),
+        _p(x), _dt(x, "x"), ldx, _p(weight), _p(gate), _dt(gate, "gate") if gate is not None else 0, ldg, _p(out), H * O, T, H,
+        O, I, 1 if gate_per_head else 0, _stream()),
         f"head_linear T={T} H={H} {O}x{I}", nbytes=(T * H * (I + O) + H * O * I) * x.element_size(), flops=2 * T * H * O * I)
     return out
 
@@ -215,6 +218,38 @@ def store_rows_paged(rows: torch.Tensor, pages: torch.Tensor, step, block_table:
     _check(_fn("recurrent", "plm_store_rows_paged")(
         _p(rows), _dt(rows, "rows"), ld, _p(pages), _p(step.tok_pos), _p(step.tok_seq), _p(block_table),
         block_table.shape[1], T, R, _stream()), f"store_rows_paged T={T} R={R}", nbytes=2 * T * R * rows.element_size())
+
+
+def latent_store(rows: torch.Tensor, weight: torch.Tensor, eps: float, rotation, n_rot: int, pages: torch.Tensor, step,
+                 block_table: torch.Tensor) -> None:
+    """A latent's row into the pages of its cache, made from the projection's columns `rows` [T, n_rot + n_norm]
+    (float32 or the run's type; a column slice will do): the first `n_rot` columns rotated by the token's position
+    (`rotation`: `ops.Rotation` over n_rot components), the other n_norm divided by their root mean square (`eps`
+    inside the root) and multiplied by `weight` (float32 [n_norm]); `pages` [n, 1, PAGE_TOKENS, R] with R >= n_rot +
+    n_norm receive [rotated | normed | zeros] at position tok_pos[t] of sequence tok_seq[t]."""
+    ld = _cols(rows, "rows")
+    _dev(pages, "pages"), _i32(block_table, "block_table")
+    T, C = rows.shape
+    n_norm = C - int(n_rot)
+    _f32(weight, "weight", n_norm)
+    R = pages.shape[-1]
+    if n_norm <= 0 or tuple(pages.shape[1:]) != (1, PAGE_TOKENS, R) or R < C:
+        raise KernelError(f"latent_store: the pages must be [n, 1, {PAGE_TOKENS}, >= {C}]")
+    cos = sin = None
+    pairing = "half"
+    if n_rot:
+        if rotation is None or rotation.cos is None or rotation.rotary_dim != n_rot:
+            raise KernelError(f"latent_store: {n_rot} rotated columns need a rotation over {n_rot} components")
+        cos, sin, pairing = rotation.cos, rotation.sin, rotation.pairing
+        if step.max_position >= cos.shape[0]:
+            raise KernelError(f"position {step.max_position} lies beyond the rotary table")
+    set_bounds("recurrent", n_pages=pages.shape[0], n_seqs=block_table.shape[0],
+               n_positions=block_table.shape[1] * PAGE_TOKENS, device=rows.device)
+    _check(_fn("recurrent", "plm_latent_store")(
+        _p(rows), _dt(rows, "rows"), ld, _p(weight), float(eps), _p(cos), _p(sin), _p(pages), _dt(pages, "pages"),
+        _p(step.tok_pos), _p(step.tok_seq), _p(block_table), block_table.shape[1], T, int(n_rot), n_norm, R,
+        0 if pairing == "half" else 1, _stream()), f"latent_store T={T} rot={n_rot} norm={n_norm}",
+        nbytes=T * (C * rows.element_size() + R * pages.element_size()))
 
 
 def rglru_gates(u: torch.Tensor, w_rate: torch.Tensor, w_in: torch.Tensor, b_rate: torch.Tensor, b_in: torch.Tensor,

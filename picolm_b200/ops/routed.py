@@ -26,11 +26,14 @@ def router_logits(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 def route_topk(logits: torch.Tensor, n_experts: int, top: int, correction: Optional[torch.Tensor] = None,
                n_groups: int = 1, keep_groups: int = 1, scale: float = 1.0,
-               gate_col: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+               gate_col: Optional[int] = None, scores: str = "sigmoid", group_score: str = "top2",
+               normalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """The choice of `top` experts per token from router logits [T, >= n_experts] (float32): scores are
-    `sigmoid(logit)`; the choice goes by score + `correction` (float32 [n_experts]), among the experts of the
+    `sigmoid(logit)` (`scores="softmax"`: the softmax over the n_experts logits); the choice goes by score +
+    `correction` (float32 [n_experts]), among the experts of the
     `keep_groups` best of `n_groups` equal groups of neighbours (a group's score: the sum of its two largest choice
-    scores); the weights are the chosen scores without the correction, divided by their sum (+ 1e-20), times `scale`.
+    scores, or with `group_score="max"` its largest); the weights are the chosen scores without the correction,
+    divided by their sum (+ 1e-20) unless `normalize` is False, times `scale`.
     Returns (ids int32 [T, top], weights float32 [T, top], gate float32 [T] = sigmoid(logits[:, gate_col]) or None)."""
     _dev(logits, "logits")
     if logits.dtype != torch.float32 or logits.dim() != 2:
@@ -43,12 +46,15 @@ def route_topk(logits: torch.Tensor, n_experts: int, top: int, correction: Optio
         _dev(correction, "correction")
         if correction.dtype != torch.float32 or correction.shape != (E,):
             raise KernelError("route_topk: correction must be float32 [experts]")
+    if scores not in ("sigmoid", "softmax") or group_score not in ("top2", "max"):
+        raise KernelError(f"route_topk: scores {scores!r} (sigmoid, softmax) or group_score {group_score!r} (top2, max) is not known")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     gate = torch.empty((T,), dtype=torch.float32, device=logits.device) if gate_col is not None else None
     _check(_fn("routed", "plm_route_topk")(
         _p(logits), ld, _p(correction), E, int(top), int(n_groups), int(keep_groups), float(scale), _p(ids), _p(weights),
-        _p(gate), int(gate_col or 0), T, _stream()), f"route_topk T={T} E={E}")
+        _p(gate), int(gate_col or 0), T, 1 if scores == "softmax" else 0, 1 if group_score == "max" else 0,
+        1 if normalize else 0, _stream()), f"route_topk T={T} E={E}")
     return ids, weights, gate
 
 
@@ -72,7 +78,9 @@ def moe_max_tiles(n_entries: int, n_experts: int, bm: int) -> int:
     return min(n_entries, (n_entries + n_experts * (bm - 1)) // bm)
 
 
-def moe_align(ids: torch.Tensor, n_experts: int, bm: int) -> SortedPairs:
+def moe_align(ids: torch.Tensor, n_experts: int, bm: int, n_skip: int = 0) -> SortedPairs:
+    """The chosen pairs `ids` [T, top] sorted by expert into tiles of `bm` rows.  Ids in [n_experts, n_experts + n_skip)
+    (experts without tensors, whose output is their input) are left out of the sort: `where` holds -1 for them."""
     _i32(ids, "ids")
     T, top = ids.shape
     n = T * top
@@ -82,7 +90,7 @@ def moe_align(ids: torch.Tensor, n_experts: int, bm: int) -> SortedPairs:
     tile_expert = torch.empty((max_tiles,), dtype=torch.int32, device=dev)
     where = torch.empty((n,), dtype=torch.int32, device=dev)
     _check(_fn("routed", "plm_moe_align")(_p(ids), n, int(n_experts), int(bm), _p(tile_expert), _p(sorted_), _p(where),
-                                          max_tiles, _stream()), f"moe_align pairs={n} E={n_experts}")
+                                          max_tiles, int(n_skip), _stream()), f"moe_align pairs={n} E={n_experts}")
     return SortedPairs(sorted_, tile_expert, where, bm, max_tiles, top, T)
 
 
@@ -131,8 +139,13 @@ def moe_gather(h: torch.Tensor, pairs: SortedPairs) -> torch.Tensor:
 
 
 def moe_combine(y: torch.Tensor, pairs: SortedPairs, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
-                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = sum_k weights[t, k] * y[row of pair (t, k)] (+ gate[t] * shared[t]): float32 [T, d], k ascending."""
+                gate: Optional[torch.Tensor] = None, ident: Optional[torch.Tensor] = None,
+                add: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sum[t] = sum_k weights[t, k] * y[row of pair (t, k)] (+ gate[t] * shared[t]): float32 [T, d], k ascending.  A pair
+    that the sort left out (an expert whose output is its input) enters as weights[t, k] * ident[t] (`ident` [T, d],
+    float32 or the run's type).  Returns `out_scale * (sum + add)` (`add`: float32 [T, d] or None), or with `into`
+    (float32 [T, d], the residual stream) adds that to it in place and returns it."""
     _dev(y, "y"), _dev(weights, "weights")
     d = y.shape[1]
     T, top = weights.shape
@@ -143,8 +156,19 @@ def moe_combine(y: torch.Tensor, pairs: SortedPairs, weights: torch.Tensor, shar
             _dev(t, n)
             if t.dtype != torch.float32 or tuple(t.shape) != shape:
                 raise KernelError(f"moe_combine: {n} must be float32 {shape}")
-    out = torch.empty((T, d), dtype=torch.float32, device=y.device)
+    for t, n in ((add, "add"), (into, "into")):
+        if t is not None:
+            _dev(t, n)
+            if t.dtype != torch.float32 or tuple(t.shape) != (T, d):
+                raise KernelError(f"moe_combine: {n} must be float32 {(T, d)}")
+    if ident is not None:
+        _dev(ident, "ident")
+        if tuple(ident.shape) != (T, d):
+            raise KernelError(f"moe_combine: ident must be {(T, d)}")
+    out = into if into is not None else torch.empty((T, d), dtype=torch.float32, device=y.device)
     _check(_fn("routed", "plm_moe_combine")(_p(y), d, _p(pairs.where), _p(weights), top, _p(shared), _p(gate), _p(out), T, d,
+                                            _p(ident), _dt(ident, "ident") if ident is not None else 0, _p(add),
+                                            float(out_scale), 1 if into is not None else 0,
                                             _stream()), f"moe_combine T={T} d={d}", nbytes=(top + 2) * T * d * 4)
     return out
 

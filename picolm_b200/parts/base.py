@@ -21,6 +21,9 @@ Families and what `forward` takes and returns (T = tokens of the step):
   head          forward(h_rows) -> logits [rows, vocab] fp32.
   token_input   forward(x, step, rows=None) -> delta fp32 from the stream's rows x (in the run's dtype) and the
                 tokens they belong to (`rows`: the step's row numbers of x's rows where the stream was narrowed).
+  row_filter    forward(h, step, cache) -> h' [T, d] in h's type: something done to a mixer's input rows that needs
+                the rows of earlier tokens (a shift towards the token before); `cache_spec()` says what it keeps
+                per sequence.
   run_input     forward(stream, index, first) adds what a run of the schedule starts with to the stream: entry
                 `index` of its own table and, with `first` (float32 rows), what the stream began as.
 """
@@ -34,7 +37,8 @@ import torch
 from ..config.spec import PartSpec
 from ..runtime import Runtime
 
-FAMILIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "embedding", "head", "token_input", "run_input")
+FAMILIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "embedding", "head", "token_input", "run_input",
+            "row_filter")
 
 
 @dataclass(frozen=True)

@@ -18,8 +18,12 @@ from __future__ import annotations
 
 from typing import List
 
+import torch
+
+from .. import ops
+from ..cache.spec import CacheSpec
 from ..config.spec import LayerSpec, PartSpec
-from .base import Part, build_part, register_part
+from .base import Part, WeightSpec, build_part, register_part
 from .stream import PostNormed, settle
 
 
@@ -32,7 +36,7 @@ class Arrangement(Part):
     narrows_rows = False
 
     def __init__(self, layer_spec: LayerSpec, runtime):
-        super().__init__({}, runtime)
+        super().__init__(dict(getattr(layer_spec, "params", None) or {}), runtime)
         self.spec = layer_spec
         missing = [n for n in self.wants if n not in layer_spec.parts]
         if missing:
@@ -163,3 +167,130 @@ def sandwich_norm_layer(prefix: str, mixer: PartSpec, mixer_norm: PartSpec, mixe
         parts.update({"feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward),
                       "feed_forward_post_norm": ("norm", feed_forward_post_norm)})
     return LayerSpec(prefix, "sandwich_norm", parts, cache_of=cache_of)
+
+
+@register_part("row_filter", "token_shift")
+class TokenShift(Part):
+    """What a mixer reads is moved towards the token before, element by element: `h_t + (h_(t-1) - h_t) * mu` with a
+    learned `mu` [size], h_(t-1) as it was before this step was applied to it, zeros before a sequence's first token.
+    The row before is part of the sequence's state.  params: size, name (the tensor of mu; default "shift", "" for
+    the prefix alone).
+
+    As a kernel this is a causal convolution over time with two taps (mu for the token before, 1 - mu for the
+    token itself); a norm that can do it on the way (`ops.norm_pair_shift`) is handed `mu` and the state instead."""
+
+    graph_safe = True
+    graph_safe_prompts = True
+
+    @property
+    def _name(self) -> str:
+        return self.params.get("name", "shift")
+
+    def weight_specs(self):
+        return {self._name: WeightSpec((self.params["size"],), init="uniform", lo=0.0, hi=1.0)}
+
+    def load(self, tensors):
+        self.mu = tensors[self._name].to(torch.float32).contiguous()
+        self.taps = torch.stack([self.mu, 1.0 - self.mu]).contiguous()          # [2, size]: the token before, the token
+
+    def weight_bytes(self):
+        return 4 * self.mu.numel()
+
+    def cache_spec(self):
+        return CacheSpec.state((self.params["size"],), private=True)
+
+    def forward(self, h, step, cache):
+        return ops.causal_conv(h, self.taps, None, cache.state, step, activation=None)
+
+
+@register_part("arrangement", "parallel_norm")
+class ParallelNormBlock(Arrangement):
+    """Mixer and feed-forward side by side, each behind a norm of its own of the same x:
+    `x += scale * (mixer(filter(norm_a(x))) + feed_forward(norm_b(x)))`.  The feed-forward with its norm and the
+    filter (family "row_filter": something done to the mixer's input alone) are optional; `scale` is the layer's
+    `params["residual_scale"]` (default 1).
+
+    Both norms are RMS norms here, so that one pass over a row serves both (and a `token_shift` filter with them:
+    `ops.norm_pair_shift`); other norms run one after the other.  A feed-forward that can (`adds_to_stream`) puts
+    `scale * (its own result + the mixer's)` into the stream itself."""
+
+    wants = ("mixer_norm", "mixer")
+    narrows_rows = True
+
+    def __init__(self, layer_spec, runtime):
+        super().__init__(layer_spec, runtime)
+        self.scale = float(self.params.get("residual_scale", 1.0))
+
+    def _caches(self, caches):
+        """(the filter's cache, what the mixer is handed) of the layer's caches, which come in the order of the parts."""
+        caches = list(caches or [])
+        owners = self.cache_owners()
+        filt = caches.pop(0) if owners and owners[0] == "mixer_filter" else None
+        if hasattr(self.mixer, "cache_specs"):
+            return filt, caches
+        return filt, (caches[0] if caches else None)
+
+    def _fused_norms(self) -> bool:
+        from .norm import RMSNorm
+        norms = [self.mixer_norm] + ([self.feed_forward_norm] if "feed_forward" in self.named else [])
+        filt = self.named.get("mixer_filter")
+        return (all(isinstance(n, RMSNorm) and n.weight.dtype == torch.float32 for n in norms)
+                and len({float(n.params["eps"]) for n in norms}) == 1 and (filt is None or isinstance(filt, TokenShift)))
+
+    def forward(self, stream, step, caches, keep_rows=None):
+        dt = self.runtime.dtype
+        filt_cache, mixer_cache = self._caches(caches)
+        filt = self.named.get("mixer_filter")
+        has_ff = "feed_forward" in self.named
+        if keep_rows is not None and keep_rows.numel() == 0:
+            has_ff = False                                            # nothing reads what this layer adds to the stream
+        h_ff = None
+        if self._fused_norms():
+            settle(stream, None)                                      # x += what the layer before left
+            h, h_ff = ops.norm_pair_shift(
+                stream.x, self.mixer_norm.weight, float(self.mixer_norm.params["eps"]), dt,
+                w_b=self.feed_forward_norm.weight if has_ff and keep_rows is None else None,
+                mix=filt.mu if filt is not None else None, state=filt_cache.state if filt is not None else None, step=step)
+        else:
+            h = self.mixer_norm.forward(stream)
+            if has_ff and keep_rows is None:
+                h_ff = self.feed_forward_norm.forward(stream)
+            if filt is not None:
+                h = filt.forward(h, step, filt_cache)
+        delta = self.mixer.forward(h, step, mixer_cache)
+        if keep_rows is not None:
+            # the last layer of a step: once the mixer has seen all tokens only these rows matter
+            if keep_rows.numel() == 0:
+                stream.pending = None
+                return
+            stream.pending = delta
+            stream.narrow(keep_rows)
+            delta, stream.pending = stream.pending, None
+            if has_ff:
+                h_ff = self.feed_forward_norm.forward(stream)
+        if hasattr(delta, "compute"):
+            delta = delta.compute()
+        if not has_ff:
+            stream.pending = delta if self.scale == 1.0 else ops.scaled_sum(delta, self.scale, delta, 0.0)
+            return
+        if getattr(self.feed_forward, "adds_to_stream", False):
+            self.feed_forward.forward(h_ff, step, add=delta, out_scale=self.scale, into=stream.x)
+            return
+        other = self.feed_forward.forward(h_ff, step)
+        if hasattr(other, "compute"):
+            other = other.compute()
+        stream.pending = ops.scaled_sum(delta, self.scale, other, self.scale)
+
+
+def parallel_norm_layer(prefix: str, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: PartSpec = None,
+                        feed_forward_norm: PartSpec = None, mixer_filter: PartSpec = None, residual_scale: float = 1.0,
+                        cache_of=None) -> LayerSpec:
+    """The spec of a `parallel_norm` layer; without `feed_forward` the layer only mixes.  `mixer_filter`: a part of
+    the "row_filter" family between the mixer's norm and the mixer."""
+    parts = {"mixer_norm": ("norm", mixer_norm)}
+    if mixer_filter is not None:
+        parts["mixer_filter"] = ("row_filter", mixer_filter)          # (in front of the mixer: the order of the layer's caches)
+    parts["mixer"] = ("mixer", mixer)
+    if feed_forward is not None:
+        parts.update({"feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward)})
+    return LayerSpec(prefix, "parallel_norm", parts, cache_of=cache_of, params={"residual_scale": float(residual_scale)})

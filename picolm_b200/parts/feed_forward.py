@@ -79,13 +79,22 @@ class RoutedMLP(Part):
     {"size", "prefix", "gate"}: the shared expert's inner width, its tensors' prefix, and the name under that prefix of
     the [1, hidden] row whose sigmoid multiplies the shared expert's result per token; None: no such gate).
 
+    Optional: scores ("sigmoid", or "softmax": over all router outputs), group_score ("top2", or "max": a group's
+    score is its best choice score), normalize (False: the weights are the chosen scores as they are, times
+    `route_scale`), identity (a number: the router has that many outputs more, behind the experts', for experts
+    without tensors whose output is their input; they take part in scores, groups and choice like the others).
+
     The router's logits are a float32 product; scores are `sigmoid(logit)`; the weights of the chosen experts are
     their scores (without the correction) divided by their sum (+ 1e-20), times `route_scale`.  The choice stays on
     the device: the chosen (token, expert) pairs are sorted by expert into tiles, and the experts' products run over
-    those tiles (`ops/routed.py`)."""
+    those tiles (`ops/routed.py`).
+
+    `forward(h, step, add=, out_scale=, into=)`: the weighted sum can take a sublayer's float32 rows beside it, a
+    factor on the sum of both, and the residual stream to add the result to (`adds_to_stream`)."""
 
     graph_safe = True
     graph_safe_prompts = True
+    adds_to_stream = True
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -93,11 +102,18 @@ class RoutedMLP(Part):
         self.E, self.top, self.F, self.d = int(p["experts"]), int(p["top"]), int(p["expert_size"]), int(p["hidden_size"])
         g = p.get("groups")
         self.n_groups, self.keep = (int(g["count"]), int(g["keep"])) if g else (1, 1)
-        if not 0 < self.top <= self.E or self.E % self.n_groups or not 0 < self.keep <= self.n_groups:
-            raise ValueError(f"routed_mlp: top={self.top}, experts={self.E}, groups={self.n_groups}, kept={self.keep} "
-                             f"do not fit together")
-        if self.top > self.keep * (self.E // self.n_groups):
-            raise ValueError(f"routed_mlp: {self.keep} groups of {self.E // self.n_groups} experts cannot give {self.top} choices")
+        self.identity = int(p.get("identity") or 0)
+        self.n_out = self.E + self.identity                  # the router's outputs: experts, then identity experts
+        self.scores, self.group_score = p.get("scores", "sigmoid"), p.get("group_score", "top2")
+        self.normalize = bool(p.get("normalize", True))
+        if self.scores not in ("sigmoid", "softmax") or self.group_score not in ("top2", "max"):
+            raise ValueError(f"routed_mlp: scores={self.scores!r} (sigmoid, softmax) or group_score={self.group_score!r} "
+                             f"(top2, max) is not known")
+        if not 0 < self.top <= self.n_out or self.n_out % self.n_groups or not 0 < self.keep <= self.n_groups or self.identity < 0:
+            raise ValueError(f"routed_mlp: top={self.top}, router outputs={self.n_out}, groups={self.n_groups}, "
+                             f"kept={self.keep} do not fit together")
+        if self.top > self.keep * (self.n_out // self.n_groups):
+            raise ValueError(f"routed_mlp: {self.keep} groups of {self.n_out // self.n_groups} experts cannot give {self.top} choices")
         self.shared = None
         sh = p.get("shared")
         if sh:
@@ -109,9 +125,9 @@ class RoutedMLP(Part):
 
     def weight_specs(self):
         p = self.params
-        specs = {p["router_name"]: WeightSpec((self.E, self.d))}
+        specs = {p["router_name"]: WeightSpec((self.n_out, self.d))}
         if p.get("correction_name"):
-            specs[p["correction_name"]] = WeightSpec((self.E,), init="normal")
+            specs[p["correction_name"]] = WeightSpec((self.n_out,), init="normal")
         for e in range(self.E):
             specs[self._expert(e, "gate_name")] = WeightSpec((self.F, self.d))
             specs[self._expert(e, "up_name")] = WeightSpec((self.F, self.d))
@@ -133,7 +149,7 @@ class RoutedMLP(Part):
             self.shared.load({rel: tensors[f"{sh['prefix']}.{rel}"] for rel in self.shared.weight_specs()})
             if sh.get("gate"):
                 rows.append(tensors[f"{sh['prefix']}.{sh['gate']}"])
-                self.gate_col = self.E
+                self.gate_col = self.n_out
         # the router and the shared expert's gate as one float32 product: [experts (+ 1), hidden]
         self.w_router = _stack_rows(rows)
         self.correction = (tensors[p["correction_name"]].to(torch.float32).contiguous() if p.get("correction_name") else None)
@@ -156,27 +172,30 @@ class RoutedMLP(Part):
         return (self.w_router.numel() * self.w_router.element_size() + min(self.E, tokens * self.top) * per
                 + (self.shared.weight_bytes() if self.shared is not None else 0))
 
-    def forward(self, h, step):
+    def forward(self, h, step, add=None, out_scale: float = 1.0, into=None):
         if hasattr(h, "materialize"):
             h = h.materialize()
         T = h.shape[0]
         logits = ops.router_logits(h, self.w_router)
-        ids, weights, gate = ops.route_topk(logits, self.E, self.top, self.correction, self.n_groups, self.keep,
-                                            float(self.params["route_scale"]), self.gate_col)
+        ids, weights, gate = ops.route_topk(logits, self.n_out, self.top, self.correction, self.n_groups, self.keep,
+                                            float(self.params["route_scale"]), self.gate_col, scores=self.scores,
+                                            group_score=self.group_score, normalize=self.normalize)
+        skip = self.identity
         if self.interleaved and T * self.top >= 64 * self.E and ops.moe_tc_supported(h, self.w_gate_up, self.w_down):
             # many pairs an expert (prompts): tiles of 128 rows on tcgen05, the tokens' rows laid out in sorted order first
-            pairs = ops.moe_align(ids, self.E, 128)
+            pairs = ops.moe_align(ids, self.E, 128, skip)
             act = ops.moe_gate_up_tc(ops.moe_gather(h, pairs), self.w_gate_up, pairs)
             y = ops.moe_down_tc(act, self.w_down, pairs)
         else:
             # few pairs an expert (decode steps): small tiles, so that a tile's padding costs little; bfloat16 on
             # mma.sync, float32 on the CUDA cores (which take tiles of 64 rows where experts have many)
             bm = 16 if (h.dtype == torch.bfloat16 or T * self.top <= 16 * self.E) else 64
-            pairs = ops.moe_align(ids, self.E, bm)
+            pairs = ops.moe_align(ids, self.E, bm, skip)
             act = ops.moe_gate_up(h, self.w_gate_up, pairs, interleaved=self.interleaved)
             y = ops.moe_down(act, self.w_down, pairs)
         shared = None
         if self.shared is not None:
             shared = self.shared.forward(h, step)
             shared = shared.compute() if hasattr(shared, "compute") else shared
-        return ops.moe_combine(y, pairs, weights, shared, gate)
+        return ops.moe_combine(y, pairs, weights, shared, gate, ident=h if skip else None, add=add, out_scale=out_scale,
+                               into=into)

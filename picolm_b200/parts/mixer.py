@@ -52,6 +52,15 @@ class Attention(Part):
                     key and no value that the scale does not touch
       own_kv        False: the layer has no key and value tensors (projections, biases, key norm); it attends over
                     what the layer it borrows its cache from wrote
+      sink_value    a number instead of a tensor: every head's denominator also holds exp(sink_value) (0: one more 1)
+      gate_name     a tensor [num_heads * value_dim, hidden]: the concatenated heads are multiplied element by element
+                    by sigmoid(W_g h) before the output projection (W_g rides in the QKV product)
+      conv          {"taps", "suffix"}: a short causal convolution over time on every channel of q, k and v straight
+                    after the projection (before norm and rotation), no bias, no activation; tensors
+                    `<q_name|k_name|v_name><suffix>` [channels, taps], the last tap the token's own.  The last taps - 1
+                    projected rows of a sequence are kept beside the keys and values (a cache of the layer's own
+                    even where keys and values are borrowed)
+      head_scale_name  a tensor [num_heads]: head h's scores are multiplied by it (its queries are, after the rotation)
     With any of value_dim, bias, qk_norm or own_kv=False, what stands between the QKV product and attention is one
     kernel (`ops.qk_norm_rope_store`: bias, norm and rotation in float32 on the product's float32 result) and the
     cache keeps heads of one width, max(head_dim, value_dim) rounded up to 16, the narrower of keys and values padded
@@ -87,9 +96,17 @@ class Attention(Part):
         if self.v_from_k and (self.vd != self.hd or not self.own_kv):
             raise ValueError("keys that serve as values need value_dim == head_dim and keys of the layer's own")
         self.sink_name = p.get("sink_name")
+        self.sink_value = p.get("sink_value")
+        if self.sink_name is not None and self.sink_value is not None:
+            raise ValueError("attention: a learned sink and a constant one at once")
+        self.gate_name, self.head_scale_name = p.get("gate_name"), p.get("head_scale_name")
+        self.conv = p.get("conv")
+        if self.conv is not None and (int(self.conv["taps"]) < 1 or self.v_from_k):
+            raise ValueError("attention: a convolution needs at least one tap and values of their own")
         # the general form: its own kernel between the product and attention, a cache of padded heads
         self.general = (self.vd != self.hd or self.bias or self.qk_norm is not None or not self.own_kv or self.v_from_k
-                        or self.sink_name is not None)
+                        or self.sink_name is not None or self.sink_value is not None or self.gate_name is not None
+                        or self.conv is not None or self.head_scale_name is not None)
         self.hd_c = -(-max(self.hd, self.vd) // 16) * 16 if self.general else self.hd
         pos = p.get("position") or PartSpec("none")
         self.position = build_part("position", pos, runtime)
@@ -111,6 +128,14 @@ class Attention(Part):
                 specs[p["v_name"]] = WeightSpec((G * vd, d))
         if self.sink_name is not None:
             specs[self.sink_name] = WeightSpec((H,), init="normal_scaled", scale=1.0)
+        if self.gate_name is not None:
+            specs[self.gate_name] = WeightSpec((H * vd, d))
+        if self.head_scale_name is not None:
+            specs[self.head_scale_name] = WeightSpec((H,), init="uniform", lo=0.5, hi=1.5)
+        if self.conv is not None:
+            for name in self._names():
+                specs[name + self.conv.get("suffix", ".conv")] = WeightSpec((specs[name].shape[0], int(self.conv["taps"])),
+                                                                            init="normal_scaled", scale=0.5)
         if self.bias:
             sfx = p.get("bias_suffix", ".b")
             for name in self._names() + [p["o_name"]]:
@@ -123,11 +148,30 @@ class Attention(Part):
 
     def load(self, tensors):
         p = self.params
-        # one projection for q, k and v: rows [q heads | k heads | v heads]
-        self.w_qkv = _stack_rows([tensors[n] for n in self._names()])
+        # one projection for q, k and v: rows [q heads | k heads | v heads], and behind them the gate's rows
+        rows = [tensors[n] for n in self._names()]
+        self.n_qkv = sum(t.shape[0] for t in rows)
+        if self.gate_name is not None:
+            g = tensors[self.gate_name]
+            if self.hd_c != self.vd:
+                # the gate meets heads of the cache's width: rows of zeros where attention hands back zeros
+                wide = torch.zeros((self.H, self.hd_c, self.d), dtype=g.dtype, device=g.device)
+                wide[:, :self.vd] = g.view(self.H, self.vd, self.d)
+                g = wide.view(self.H * self.hd_c, self.d)
+            rows.append(g)
+        self.w_qkv = _stack_rows(rows)
         self.w_o = tensors[p["o_name"]]
         self.b_qkv = self.b_o = self.w_qn = self.w_kn = None
         self.sink = None if self.sink_name is None else tensors[self.sink_name].to(torch.float32).contiguous()
+        if self.sink_value is not None:
+            self.sink = torch.full((self.H,), float(self.sink_value), dtype=torch.float32, device=self.w_o.device)
+        self.head_scale = (None if self.head_scale_name is None
+                           else tensors[self.head_scale_name].to(torch.float32).contiguous())
+        self.w_conv = None
+        if self.conv is not None:
+            # tap-major [taps, channels] in float32, the channels in the order of the product's columns
+            sfx = self.conv.get("suffix", ".conv")
+            self.w_conv = torch.cat([tensors[n + sfx].to(torch.float32) for n in self._names()]).t().contiguous()
         if self.bias:
             sfx = p.get("bias_suffix", ".b")
             self.b_qkv = torch.cat([tensors[n + sfx].to(torch.float32) for n in self._names()]).contiguous()
@@ -149,28 +193,50 @@ class Attention(Part):
         # (chunks: pages are kept; a layer that borrows this cache may cut its chunks elsewhere)
         return CacheSpec.kv(self.G, self.hd_c, self.window)
 
+    def cache_specs(self):
+        """The keys and values, and for a convolution the last taps - 1 projected rows of every sequence (the layer's
+        own even where it borrows keys and values).  `forward` takes them in this order, or the first alone."""
+        specs = [self.cache_spec()]
+        if self.conv is not None and int(self.conv["taps"]) > 1:
+            cols = self.H * self.hd + ((self.G * self.hd + self.G * self.vd) if self.own_kv else 0)
+            specs.append(CacheSpec.state(((int(self.conv["taps"]) - 1) * cols,), private=True))
+        return specs
+
     def prepare(self, max_seq_tokens: int) -> None:
         self.position.prepare(max_seq_tokens)
 
     takes_scaled_rows = True          # h goes into a product and nowhere else
 
-    def _forward_general(self, h, step, cache):
+    def _forward_general(self, h, step, cache, conv_state=None):
         dt = self.runtime.dtype
         if self.own_kv and not cache.writable:
             raise RuntimeError("a layer that reads another layer's cache must be built with own_kv=False")
-        qkv = ops.linear(h, self.w_qkv, torch.float32)       # bias, norm and rotation work on the float32 sums
+        proj = ops.linear(h, self.w_qkv, torch.float32)      # bias, norm and rotation work on the float32 sums
+        qkv = proj[:, :self.n_qkv] if self.gate_name is not None else proj
+        if self.w_conv is not None:
+            if self.w_conv.shape[0] > 1 and conv_state is None:
+                raise RuntimeError("attention with a convolution was handed no state for it")
+            state = conv_state.state if conv_state is not None else proj     # (one tap: no state is read)
+            qkv = ops.causal_conv(qkv, self.w_conv, None, state, step, activation=None)
         q = torch.empty((h.shape[0], self.H, self.hd_c), dtype=dt, device=h.device)
         rotation = self.position.rotation() if hasattr(self.position, "rotation") else None
         ops.qk_norm_rope_store(qkv, self.b_qkv, self.w_qn, self.w_kn, self.qk_norm["eps"] if self.qk_norm else 0.0, q,
                                cache, rotation, step, self.H, self.G, self.hd, self.vd, own_kv=self.own_kv,
-                               per_head=self.per_head_norm, values_from_keys=self.v_from_k)
+                               per_head=self.per_head_norm, values_from_keys=self.v_from_k, q_scale=self.head_scale)
         ctx = ops.attention(q, cache, step, self.G, self.scale, chunk=self.chunk, sink=self.sink)
+        if self.gate_name is not None:
+            ctx = ops.gated_norm(ctx, dt, group=self.hd_c, gate=proj[:, self.n_qkv:], gate_mode=ops.GATE_AFTER_NORM,
+                                 activation="sigmoid", norm=False)
         delta = ops.linear(ctx, self.w_o, torch.float32, defer=True)
         return BiasedDelta(delta, self.b_o) if self.b_o is not None else delta
 
     def forward(self, h, step, cache):
+        conv_state = None
+        if isinstance(cache, (list, tuple)):                 # all of `cache_specs()`, in their order
+            conv_state = cache[1] if len(cache) > 1 else None
+            cache = cache[0]
         if self.general:
-            return self._forward_general(h, step, cache)
+            return self._forward_general(h, step, cache, conv_state)
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, dt)
         # a position encoding that can describe itself as a rotation (`rotation()`) may be applied, and the

@@ -16,17 +16,25 @@ from .stream import BiasedDelta, PostNormed, ResidualStream, pending_addends
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """params: size, eps, name (the weight's tensor name relative to the part's prefix; default "weight", ""
-    for a tensor that is called by the prefix alone).  Weight: [size]."""
+    for a tensor that is called by the prefix alone), one_plus (True: the weight is stored around zero and the row
+    is multiplied by 1 + w; the sum is made once, in float32, when the weights are loaded).  Weight: [size]."""
 
     @property
     def _name(self) -> str:
         return self.params.get("name", "weight")
 
+    @property
+    def one_plus(self) -> bool:
+        return bool(self.params.get("one_plus", False))
+
     def weight_specs(self):
-        return {self._name: WeightSpec((self.params["size"],), init="ones_normal")}
+        return {self._name: WeightSpec((self.params["size"],), init="normal" if self.one_plus else "ones_normal")}
 
     def load(self, tensors):
         self.weight = tensors[self._name]
+        if self.one_plus:
+            # 1 + w has more digits than the stored type holds: kept in float32 (the norm kernels take either)
+            self.weight = (1.0 + self.weight.to(torch.float32)).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
@@ -38,7 +46,12 @@ class RMSNorm(Part):
             w = self._weight_f32 = self.weight.to(torch.float32).contiguous()
         return w
 
-    can_defer_scale = True
+    @property
+    def can_defer_scale(self) -> bool:
+        """Whether the scale may be left to the products that take the result (their epilogues apply a weight of the
+        run's type, which 1 + w is not)."""
+        return not self.one_plus
+
     graph_safe = True
     graph_safe_prompts = True
 
