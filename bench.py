@@ -220,9 +220,9 @@ def main():
                     help="with the other points: one request's decode rate after a prompt of this many tokens (0: skip)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
-    ap.add_argument("--design", default="", choices=["", "potuzen", "kunulorn", "tebasun"],
+    ap.add_argument("--design", default="", choices=["", "potuzen", "kunulorn", "tebasun", "fupapel"],
                     help="instead of the headline: prefill and decode throughput of this design beside the Llama decoder "
-                         "(tebasun: beside potuzen) at equal layer sizes (random weights); prints one JSON line of its own")
+                         "(tebasun: beside potuzen; fupapel: beside kunulorn) at equal layer sizes (random weights); prints one JSON line of its own")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="with --design: which sizes (w2048, w4096)")
     ap.add_argument("--design-prompt", type=int, default=2048, help="with --design: tokens of the timed prompt")
     ap.add_argument("--design-kernels", action="store_true",

@@ -39,11 +39,10 @@ def _rope(rot, head_dim: int) -> PartSpec:
 def _mixer_spec(cfg: FupapelConfig, layer) -> PartSpec:
     m, d = layer.mixer, cfg.width
     if layer.type == "latent_attention":
-        if m["mask_size"] is not None:
-            raise ValueError("latent_attention under a mask of chunks is not laid out")
         return PartSpec("latent_attention", {
             "hidden_size": d, "heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"], "kv_rank": m["kv_rank"],
-            "q_rank": m["q_rank"], "scale": m["scale"], "window": None, "eps": cfg.norm_eps, "rot_dim": m["rot_dim"],
+            "q_rank": m["q_rank"], "scale": m["scale"], "window": None, "chunk": m["mask_size"], "eps": cfg.norm_eps,
+            "rot_dim": m["rot_dim"],
             "position": _rope(m["rot"], m["rot_dim"]), "sink_name": "sink", "gate_per_head": True}, prefix="mix")
     params = {
         "hidden_size": d, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],

@@ -1,8 +1,9 @@
-"""Throughput of another design (Potuzen, Kunulorn, Tebasun) beside the Llama decoder (Tebasun: beside Potuzen, the other
-design whose layers are recurrences and attention in turn) at equal layer sizes (random weights): prefill
+"""Throughput of another design (Potuzen, Kunulorn, Tebasun, Fupapel) beside the Llama decoder (Tebasun: beside Potuzen, the
+other design whose layers are recurrences and attention in turn; Fupapel: beside Kunulorn, the other design of chunked
+attention and routed feed-forwards) at equal layer sizes (random weights): prefill
 tokens/s of one prompt and decode tokens/s of a batch, at a few sizes that resemble a real model's layers,
 and, with `kernels=True`, the device time of every kind of launch with the fraction of the memory's or the
-tensor cores' measured rate that it reaches.  `bench.py --design potuzen|kunulorn|tebasun` calls this."""
+tensor cores' measured rate that it reaches.  `bench.py --design potuzen|kunulorn|tebasun|fupapel` calls this."""
 from __future__ import annotations
 
 import json
@@ -70,6 +71,34 @@ def tebasun_config(width: int, ff: int, layers: int, vocab: int) -> dict:
     return {"architecture": "Tebasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
             "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 1 + looped, "times": 2},
             "layers": [rglru if i in (0, n - 1) else parallel for i in range(n)]}
+
+
+def fupapel_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict:
+    """Layers in turn: gated attention with the twin's head counts (half of each head rotated), attention behind short
+    convolutions (whole heads rotated with stretched frequencies), attention through a latent (a row of 192 + 64 a
+    position), and a convolved layer that reads the keys and values of the one two before; chunks of 8,192 positions;
+    every layer routes to 4 of 30 experts (14 at the larger size) and 2 identity experts, the experts a quarter of
+    the dense width, so that a token's arithmetic is at most a dense layer's."""
+    H, G, hd = heads
+    n_out = 32 if width <= 2048 else 16
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4},
+           "router": {"experts": n_out - 2, "identity": 2, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    gated = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                            "mask": {"size": 8192}, "rot": {"base": 500000.0, "dims": hd // 2}}}
+    conv = {"type": "attention_2", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "conv": 4,
+                                             "mask": {"size": 8192},
+                                             "rot": {"base": 500000.0, "dims": hd, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0,
+                                                                                             "original": 8192}}}}
+    latent = {"type": "latent_attention", "mixer": {"heads": width // 128, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 192,
+                                                    "q_rank": width // 2, "scale": 128 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+    out = []
+    for i in range(layers):
+        layer = json.loads(json.dumps([gated, conv, latent, conv][i % 4]))
+        if i % 4 == 3:
+            layer["mixer"]["kv_from"] = i - 2
+        layer["mlp"] = mlp
+        out.append(layer)
+    return {"architecture": "Fupapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": out}
 
 
 def llama_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict:
@@ -159,10 +188,10 @@ def _table(rows, top=14):
 
 
 def run(design: str, sizes, prompt_tokens: int, batch: int, steps: int, warmup: int, kernels: bool) -> dict:
-    if design not in ("potuzen", "kunulorn", "tebasun"):
-        raise ValueError(f"no design {design!r} to compare (known: potuzen, kunulorn, tebasun)")
-    beside = "potuzen" if design == "tebasun" else "llama"
-    result = {"design": design, "beside": "Potuzen" if beside == "potuzen" else "LlamaForCausalLM", "dtype": "bf16",
+    if design not in ("potuzen", "kunulorn", "tebasun", "fupapel"):
+        raise ValueError(f"no design {design!r} to compare (known: potuzen, kunulorn, tebasun, fupapel)")
+    beside = {"tebasun": "potuzen", "fupapel": "kunulorn"}.get(design, "llama")
+    result = {"design": design, "beside": {"potuzen": "Potuzen", "kunulorn": "Kunulorn"}.get(beside, "LlamaForCausalLM"), "dtype": "bf16",
               "data": "synthetic (random weights and tokens)",
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "steps": steps, "warmup": warmup, "sizes": {}}
     for name in sizes:
@@ -170,9 +199,12 @@ def run(design: str, sizes, prompt_tokens: int, batch: int, steps: int, warmup: 
         t0 = time.time()
         config = {"potuzen": lambda: potuzen_config(width, ff, layers, vocab),
                   "kunulorn": lambda: kunulorn_config(width, ff, layers, vocab, heads),
-                  "tebasun": lambda: tebasun_config(width, ff, layers, vocab)}[design]()
+                  "tebasun": lambda: tebasun_config(width, ff, layers, vocab),
+                  "fupapel": lambda: fupapel_config(width, ff, layers, vocab, heads)}[design]()
         ours = _measure(config, prompt_tokens, batch, steps, warmup, kernels)
-        twin_config = potuzen_config(width, ff, layers, vocab) if beside == "potuzen" else llama_config(width, ff, layers, vocab, heads)
+        twin_config = {"potuzen": lambda: potuzen_config(width, ff, layers, vocab),
+                       "kunulorn": lambda: kunulorn_config(width, ff, layers, vocab, heads),
+                       "llama": lambda: llama_config(width, ff, layers, vocab, heads)}[beside]()
         twin = _measure(twin_config, prompt_tokens, batch, steps, warmup, kernels)
         result["sizes"][name] = {
             "width": width, "ff": ff, "layers": layers, design: ours, beside: twin,

@@ -173,7 +173,7 @@ class FupapelConfig:
         eps = _number(_need(_need(raw, "norm", "the model"), "eps", "norm"), "'norm.eps'")
         if eps < 0:
             raise ConfigError("config.json: 'norm.eps' must not be negative")
-        mult = _number(_need(raw, "residual_mult", "the model"), "'residual_mult'")
+        mult = _number(raw.get("residual_mult", 1.0), "'residual_mult'")          # (absent: the sum is added as it is)
         entries = _need(raw, "layers", "the model")
         if not isinstance(entries, (list, tuple)) or not entries:
             raise ConfigError("config.json: 'layers' must be a list with at least one layer")
@@ -197,7 +197,7 @@ class FupapelConfig:
                 raise ConfigError(f"config.json: layers[{i}].mixer.kv_from={j} does not name an earlier layer of its kind "
                                   f"with keys and values of its own")
             a, b = layer.mixer, layers[j].mixer
-            for key in ("heads", "kv_heads", "dim", "vdim", "rot"):
+            for key in ("kv_heads", "dim", "vdim"):           # what the cache's rows are made of
                 if a[key] != b[key]:
                     raise ConfigError(f"config.json: layers[{i}] uses the keys and values of layers[{j}] but its {key} differs")
         return FupapelConfig(vocab, width, eps, mult, tuple(layers))

@@ -691,7 +691,9 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                           const int* __restrict__ block_table, int max_pages, int H, int G, int D, int Dv, int hd_c,
                           int rot_dim, int pairing, int own_kv, int per_head, int v_from_k, long ld,
-                          const float* __restrict__ q_scale) {
+                          const float* __restrict__ q_scale, const float* __restrict__ conv_w, int taps,
+                          float* __restrict__ conv_state, long state_stride, const int* __restrict__ seq_start,
+                          const int* __restrict__ seq_slot, int conv_keeps_state) {
     extern __shared__ float qk_sm[];                 // [nq + nk]
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -701,9 +703,50 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
     const int nq = H * D, nk = own_kv ? G * D : 0, nv = own_kv && !v_from_k ? G * Dv : 0;
     const int pos = PLM_POSITION(tok_pos[t]);
     const Ta* row = qkv + (size_t)t * ld;           // (ld >= nq + nk + nv: the product may hold more columns behind them)
+    // conv_w [taps][nq + nk + nv] (tap-major, the token's own tap last): every column is first convolved over time with
+    // the projected rows of the sequence's tokens before, which lie in the rows above this one or, for tokens before the
+    // step's first, in conv_state [slot][taps - 1][columns] (oldest first).  With conv_keeps_state (a step of one token a
+    // sequence) the thread that reads a column's state also moves it on; otherwise a kernel of its own does that afterwards.
+    const int n_cols = nq + nk + nv;
+    int in_seq = 0;
+    float* conv_st = nullptr;
+    if (conv_w) {
+        const int b = PLM_SEQ_NO(tok_seq[t]);
+        in_seq = t - seq_start[b];
+        conv_st = conv_state + (long)seq_slot[b] * state_stride;
+    }
+    auto column = [&](int c) -> float {
+        if (!conv_w) return to_f32<Ta>(row[c]);
+        float acc = 0.f;
+        if (taps <= 8) {
+            // all taps' inputs asked for at once, then the sum in the same order
+            float u[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int back = taps - 1 - j, li = in_seq - back;
+                u[j] = 0.f;
+                if (j < taps) u[j] = li >= 0 ? to_f32<Ta>(qkv[(size_t)(t - back) * ld + c]) : conv_st[(long)(taps - 1 + li) * n_cols + c];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < taps) {
+                    acc = fmaf(conv_w[(long)j * n_cols + c], u[j], acc);
+                    if (conv_keeps_state && j > 0) conv_st[(long)(j - 1) * n_cols + c] = u[j];
+                }
+            }
+            return acc;
+        }
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j, li = in_seq - back;
+            const float u = li >= 0 ? to_f32<Ta>(qkv[(size_t)(t - back) * ld + c]) : conv_st[(long)(taps - 1 + li) * n_cols + c];
+            acc = fmaf(conv_w[(long)j * n_cols + c], u, acc);
+            if (conv_keeps_state && j > 0) conv_st[(long)(j - 1) * n_cols + c] = u;
+        }
+        return acc;
+    };
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < nq + nk; i += NT) {
-        float v = to_f32<Ta>(row[i]);
+        float v = column(i);
         if (bias) v += bias[i];
         qk_sm[i] = v;
         if (i < nq) sq += v * v; else sk += v * v;
@@ -785,11 +828,31 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
             if (v_from_k) {
                 if (c < D) v = qk_sm[nq + g * D + c];
             } else if (c < Dv) {
-                v = to_f32<Ta>(row[nq + nk + g * Dv + c]);
+                v = column(nq + nk + g * Dv + c);
                 if (bias) v += bias[nq + nk + g * Dv + c];
             }
             vc[((page_base + g) * PLM_PAGE + in_page) * hd_c + c] = from_f32<Tc>(v);
         }
+    }
+}
+
+// The convolution's tail after a step of several tokens a sequence: the last taps - 1 projected rows of every sequence,
+// oldest first (old tail rows move up where the step brought fewer).  One thread per (sequence, column); it reads what
+// it needs of the old tail before it writes (ascending s: slot s takes old slot s + n > s).
+template <typename Ta>
+__global__ void conv_tail_kernel(const Ta* __restrict__ qkv, long ld, float* __restrict__ state, long state_stride,
+                                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int n_seqs, int C, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_seqs * C) return;
+    const int b = (int)(idx / C), c = (int)(idx % C);
+    const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
+    if (n <= 0) return;
+    float* st = state + (long)seq_slot[b] * state_stride;
+    for (int s = 0; s < taps - 1; ++s) {
+        const int src = n - (taps - 1) + s;
+        st[(long)s * C + c] = src >= 0 ? to_f32<Ta>(qkv[(size_t)(t0 + src) * ld + c]) : st[(long)(s + n) * C + c];
     }
 }
 
@@ -799,8 +862,16 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
                                       const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
                                       int max_pages, int n_tokens, int H, int G, int D, int Dv, int hd_c, int rot_dim,
                                       int pairing, int own_kv, int per_head, int v_from_k, long ld, const float* q_scale,
+                                      const float* conv_w, int taps, float* conv_state, long state_stride,
+                                      const int* seq_start, const int* seq_slot, int n_seqs, int one_token_each,
                                       cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
+    const int conv_cols = H * D + (own_kv ? G * D + (v_from_k ? 0 : G * Dv) : 0);
+    if (conv_w != nullptr && (taps < 1 || bias != nullptr || (taps > 1 && (conv_state == nullptr || seq_start == nullptr ||
+        seq_slot == nullptr || n_seqs <= 0 || state_stride < (long)(taps - 1) * conv_cols))))
+        return PLM_ERR_SHAPE;
+    // one token a sequence: the block that reads a sequence's tail also writes it
+    const int conv_keeps_state = conv_w != nullptr && one_token_each && n_seqs == n_tokens ? 1 : 0;
     if (ld < (long)H * D + (own_kv ? (long)G * D + (v_from_k ? 0 : (long)G * Dv) : 0)) return PLM_ERR_SHAPE;
     if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || hd_c < D || hd_c < Dv || (hd_c & 1) || rot_dim < 0 || rot_dim > D ||
         (rot_dim & 1))
@@ -812,10 +883,15 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
     do {                                                                                                               \
         if (smem > 48 * 1024)                                                                                          \
             cudaFuncSetAttribute(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        return plm_status_of(launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
+        cudaError_t e_ = launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
                                         (const Ta_*)qkv, bias, (const Tc_*)wq, (const Tc_*)wk, eps, (Tc_*)q_out, (Tc_*)kc, \
                                         (Tc_*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table, max_pages, H, G, D, Dv,  \
-                                        hd_c, rot_dim, pairing, own_kv, per_head, v_from_k, ld, q_scale));             \
+                                        hd_c, rot_dim, pairing, own_kv, per_head, v_from_k, ld, q_scale, conv_w, taps,  \
+                                        conv_state, state_stride, seq_start, seq_slot, conv_keeps_state);              \
+        if (e_ != cudaSuccess || conv_w == nullptr || taps == 1 || conv_keeps_state) return plm_status_of(e_);         \
+        return plm_status_of(launch_pdl(conv_tail_kernel<Ta_>, dim3((unsigned)(((long)n_seqs * conv_cols + 255) / 256)), \
+                                        dim3(256), 0, stream, (const Ta_*)qkv, ld, conv_state, state_stride, seq_start, \
+                                        seq_slot, n_seqs, conv_cols, taps));                                           \
     } while (0)
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_F32) QKN_LAUNCH(float, float);
     if (qkv_dtype == PLM_F32 && out_dtype == PLM_BF16) QKN_LAUNCH(float, bf16);
@@ -1057,16 +1133,96 @@ norm_pair_shift_kernel(const float* __restrict__ x, const float* __restrict__ w_
     }
 }
 
+// The same with rows whose width is a multiple of 4 and at most 16 * NT: four elements at a time, both rows in registers
+// between the sums of squares and the results, so that x is read once.
+template <typename To, int NT>
+__global__ void __launch_bounds__(NT)
+norm_pair_shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ w_a, const float* __restrict__ w_b,
+                           const float* __restrict__ mix, float* __restrict__ state, long state_stride,
+                           const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                           To* __restrict__ out_a, To* __restrict__ out_b, int d, float eps) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int first = 0, other = -1;
+    float* st = nullptr;
+    if (mix) {
+        const int b = PLM_SEQ_NO(tok_seq[t]);
+        first = t == seq_start[b];
+        other = first ? seq_start[b + 1] - 1 : t - 1;
+        if (other == t) other = -1;
+        st = state + (long)seq_slot[b] * state_stride;
+    }
+    const float* xr = x + (size_t)t * d;
+    const float* xo = x + (size_t)(other < 0 ? t : other) * d;
+    float4 v[4], u[4];
+    float ss = 0.f, so = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            v[k] = load4(xr + i);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+            if (other >= 0) {
+                u[k] = load4(xo + i);
+                so += u[k].x * u[k].x + u[k].y * u[k].y + u[k].z * u[k].z + u[k].w * u[k].w;
+            }
+        }
+    }
+    const float r = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)d + eps);
+    float ro = r;
+    if (other >= 0) ro = 1.0f / sqrtf(block_sum<NT>(so, red) / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i >= d) continue;
+        const float4 wa = load4(w_a + i);
+        const float4 a = make_float4(v[k].x * r * wa.x, v[k].y * r * wa.y, v[k].z * r * wa.z, v[k].w * r * wa.w);
+        float4 o = a;
+        if (mix) {
+            float4 kept = a;                       // the row that goes into the state: the sequence's last of the step
+            if (other >= 0) kept = make_float4(u[k].x * ro * wa.x, u[k].y * ro * wa.y, u[k].z * ro * wa.z, u[k].w * ro * wa.w);
+            const float4 prev = first ? load4(st + i) : kept;
+            const float4 m = load4(mix + i);
+            o = make_float4(a.x + (prev.x - a.x) * m.x, a.y + (prev.y - a.y) * m.y, a.z + (prev.z - a.z) * m.z, a.w + (prev.w - a.w) * m.w);
+            if (first) store4(st + i, kept);
+        }
+        store4(out_a + (size_t)t * d + i, o);
+        if (out_b) {
+            const float4 wb = load4(w_b + i);
+            store4(out_b + (size_t)t * d + i, make_float4(v[k].x * r * wb.x, v[k].y * r * wb.y, v[k].z * r * wb.z, v[k].w * r * wb.w));
+        }
+    }
+}
+
+template <typename To>
+static int norm_pair_shift_launch(const float* x, const float* w_a, const float* w_b, const float* mix, float* state,
+                                  long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot, void* out_a,
+                                  void* out_b, int n_tokens, int d, float eps, cudaStream_t stream) {
+    const bool aligned = (((uintptr_t)x | (uintptr_t)w_a | (uintptr_t)w_b | (uintptr_t)mix | (uintptr_t)state) & 15) == 0 &&
+                         (((uintptr_t)out_a | (uintptr_t)out_b) & 7) == 0 && state_stride % 4 == 0;
+    // (which kernel runs, and with it the order of the sums, depends on the row's width and on alignments that a model fixes)
+    if (d % 4 == 0 && aligned && d <= 16 * 256)
+        return plm_status_of(launch_pdl(norm_pair_shift_vec_kernel<To, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
+                                        state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
+    if (d % 4 == 0 && aligned && d <= 16 * 1024)
+        return plm_status_of(launch_pdl(norm_pair_shift_vec_kernel<To, 1024>, dim3(n_tokens), dim3(1024), 0, stream, x, w_a, w_b,
+                                        mix, state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
+    return plm_status_of(launch_pdl(norm_pair_shift_kernel<To, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
+                                    state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
+}
+
 extern "C" int plm_norm_pair_shift(const float* x, const float* w_a, const float* w_b, const float* mix, float* state,
                                    long state_stride, const int* tok_seq, const int* seq_start, const int* seq_slot, void* out_a,
                                    void* out_b, int out_dtype, int n_tokens, int d, float eps, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (d <= 0 || (mix != nullptr && (state == nullptr || state_stride < d))) return PLM_ERR_SHAPE;
     if (out_dtype == PLM_F32)
-        return plm_status_of(launch_pdl(norm_pair_shift_kernel<float, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
-                                        state, state_stride, tok_seq, seq_start, seq_slot, (float*)out_a, (float*)out_b, d, eps));
+        return norm_pair_shift_launch<float>(x, w_a, w_b, mix, state, state_stride, tok_seq, seq_start, seq_slot, out_a, out_b,
+                                             n_tokens, d, eps, stream);
     if (out_dtype == PLM_BF16)
-        return plm_status_of(launch_pdl(norm_pair_shift_kernel<bf16, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
-                                        state, state_stride, tok_seq, seq_start, seq_slot, (bf16*)out_a, (bf16*)out_b, d, eps));
+        return norm_pair_shift_launch<bf16>(x, w_a, w_b, mix, state, state_stride, tok_seq, seq_start, seq_slot, out_a, out_b,
+                                            n_tokens, d, eps, stream);
     return PLM_ERR_DTYPE;
 }

@@ -861,17 +861,31 @@ extern "C" int plm_store_rows_paged(const void* rows, int dtype, long ld, void* 
 // stride ld hold `n_rot` columns that are rotated by the token's position (half-split or neighbouring pairs; a key part
 // that all heads share) and then `n_norm` columns that are divided by their root mean square (eps inside the root) and
 // multiplied by w [n_norm] (fp32); the page's row is [rotated | normed | zeros] of width R >= n_rot + n_norm.  Everything
-// in fp32; one warp per token, the sum of squares in an order that depends on n_norm only.
+// in fp32; one warp per token, the sum of squares in an order that depends on n_norm only.  The same warp can norm a second
+// stretch of the token's row on the way (the queries' latent, which the same product made): q_rows [T, n_q] with stride
+// ldq, divided by their root mean square and multiplied by wq [n_q], to q_out [T, n_q] (contiguous).
 template <typename Ti, typename To>
 __global__ void __launch_bounds__(128)
 latent_store_kernel(const Ti* __restrict__ rows, long ld, const float* __restrict__ w, float eps, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, To* __restrict__ pages, const int* __restrict__ tok_pos,
                     const int* __restrict__ tok_seq, const int* __restrict__ block_table, int pages_per_seq, int n_tokens,
-                    int n_rot, int n_norm, int R, int pairing) {
+                    int n_rot, int n_norm, int R, int pairing, int store, const Ti* __restrict__ q_rows, long ldq,
+                    const float* __restrict__ wq, To* __restrict__ q_out, int n_q) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= n_tokens) return;
+    if (q_rows) {
+        const Ti* qs = q_rows + (long)t * ldq;
+        float sq = 0.f;
+        for (int j = lane; j < n_q; j += 32) {
+            const float v = to_f32<Ti>(qs[j]);
+            sq = fmaf(v, v, sq);
+        }
+        const float rq = 1.0f / sqrtf(warp_sum(sq) / (float)n_q + eps);
+        for (int j = lane; j < n_q; j += 32) q_out[(long)t * n_q + j] = from_f32<To>(to_f32<Ti>(qs[j]) * rq * wq[j]);
+    }
+    if (!store) return;
     const int pos = PLM_POSITION(tok_pos[t]);
     const int page = PLM_PAGE_NO(block_table[(long)PLM_SEQ_NO(tok_seq[t]) * pages_per_seq + pos / PLM_PAGE]);
     const Ti* src = rows + (long)t * ld;
@@ -897,16 +911,19 @@ latent_store_kernel(const Ti* __restrict__ rows, long ld, const float* __restric
 extern "C" int plm_latent_store(const void* rows, int in_dtype, long ld, const float* w, float eps, const float* cos_t,
                                 const float* sin_t, void* pages, int out_dtype, const int* tok_pos, const int* tok_seq,
                                 const int* block_table, int pages_per_seq, int n_tokens, int n_rot, int n_norm, int R,
-                                int pairing, cudaStream_t stream) {
+                                int pairing, int store, const void* q_rows, long ldq, const float* wq, void* q_out, int n_q,
+                                cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (n_rot < 0 || (n_rot & 1) || n_norm <= 0 || R < n_rot + n_norm || ld < n_rot + n_norm || (n_rot > 0 && cos_t == nullptr))
         return PLM_ERR_SHAPE;
+    if (q_rows != nullptr && (n_q <= 0 || ldq < n_q || wq == nullptr || q_out == nullptr)) return PLM_ERR_SHAPE;
+    if (!store && q_rows == nullptr) return PLM_OK;
     if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)((n_tokens + 3) / 4));
 #define LS_LAUNCH(Ti_, To_)                                                                                                     \
     return plm_status_of(launch_pdl(latent_store_kernel<Ti_, To_>, grid, dim3(128), 0, stream, (const Ti_*)rows, ld, w, eps, cos_t, \
                                     sin_t, (To_*)pages, tok_pos, tok_seq, block_table, pages_per_seq, n_tokens, n_rot, n_norm, R, \
-                                    pairing))
+                                    pairing, store, (const Ti_*)q_rows, ldq, wq, (To_*)q_out, n_q))
     if (in_dtype == PLM_F32 && out_dtype == PLM_F32) LS_LAUNCH(float, float);
     if (in_dtype == PLM_F32 && out_dtype == PLM_BF16) LS_LAUNCH(float, bf16);
     if (in_dtype == PLM_BF16 && out_dtype == PLM_BF16) LS_LAUNCH(bf16, bf16);

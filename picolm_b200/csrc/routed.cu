@@ -512,6 +512,63 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const 
         }
         return;
     }
+    // The general form.  A token's rows and weights are looked up once (up to 8 choices in registers), then four columns a
+    // thread and step where the rows allow it: the same sums in the same order as one column at a time.
+    constexpr int MAXK = 8;
+    int rows_k[MAXK];
+    float w_k[MAXK];
+    if (top <= MAXK) {
+#pragma unroll
+        for (int k = 0; k < MAXK; ++k) {
+            rows_k[k] = k < top ? where[(size_t)t * top + k] : -1;
+            w_k[k] = k < top ? weights[(size_t)t * top + k] : 0.f;
+        }
+    }
+    const float gt = shared ? (gate ? gate[t] : 1.0f) : 0.f;
+    const bool vec = top <= MAXK && d % 4 == 0 && ldy % 4 == 0 && sizeof(Th) == 4 &&
+                     ((((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out | (uintptr_t)add | (uintptr_t)ident) & 15) == 0);
+    const bool vec_bf = top <= MAXK && d % 4 == 0 && ldy % 4 == 0 && sizeof(Th) == 2 &&
+                        ((((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out | (uintptr_t)add) & 15) == 0) && (((uintptr_t)ident & 7) == 0);
+    if (vec || vec_bf) {
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float4 idv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ident) {
+                if (sizeof(Th) == 4) {
+                    idv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ident) + (size_t)t * d + i);
+                } else {
+                    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(ident) + (size_t)t * d + i);
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+                    idv = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+                }
+            }
+            float4 v[MAXK];
+#pragma unroll
+            for (int k = 0; k < MAXK; ++k)
+                if (k < top) v[k] = rows_k[k] >= 0 ? *reinterpret_cast<const float4*>(y + (size_t)rows_k[k] * ldy + i) : idv;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < MAXK; ++k)
+                if (k < top) {
+                    acc.x = fmaf(w_k[k], v[k].x, acc.x); acc.y = fmaf(w_k[k], v[k].y, acc.y);
+                    acc.z = fmaf(w_k[k], v[k].z, acc.z); acc.w = fmaf(w_k[k], v[k].w, acc.w);
+                }
+            if (shared) {
+                const float4 sv = *reinterpret_cast<const float4*>(shared + (size_t)t * d + i);
+                acc.x = fmaf(gt, sv.x, acc.x); acc.y = fmaf(gt, sv.y, acc.y); acc.z = fmaf(gt, sv.z, acc.z); acc.w = fmaf(gt, sv.w, acc.w);
+            }
+            if (add) {
+                const float4 av = *reinterpret_cast<const float4*>(add + (size_t)t * d + i);
+                acc.x += av.x; acc.y += av.y; acc.z += av.z; acc.w += av.w;
+            }
+            acc.x *= out_scale; acc.y *= out_scale; acc.z *= out_scale; acc.w *= out_scale;
+            if (accumulate) {
+                const float4 ov = *reinterpret_cast<const float4*>(out + (size_t)t * d + i);
+                acc.x += ov.x; acc.y += ov.y; acc.z += ov.z; acc.w += ov.w;
+            }
+            *reinterpret_cast<float4*>(out + (size_t)t * d + i) = acc;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {

@@ -24,10 +24,10 @@ _SIGNATURES = {
     "plm_layernorm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_add_bias": [_vp, _vp, _i, _i, _vp],
     "plm_qk_norm_rope_store": [_vp, _i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                               _i, _i, _i, _i, _i, _i, _l, _vp, _vp],
+                               _i, _i, _i, _i, _i, _i, _l, _vp, _vp, _i, _vp, _l, _vp, _vp, _i, _i, _vp],
     "plm_rope_rows": [_vp, _i, _l, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_norm_pair_shift": [_vp, _vp, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
-    "plm_latent_store": [_vp, _i, _l, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "plm_latent_store": [_vp, _i, _l, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _l, _vp, _vp, _i, _vp],
     "plm_dyt_norm": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp],
     "plm_add_rows": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "plm_scaled_sum": [_vp, _f, _vp, _vp, _f, _vp, _i, _i, _vp],

@@ -207,7 +207,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
                        k_norm: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, kv, rotation, step,
                        num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, own_kv: bool = True,
                        per_head: bool = False, values_from_keys: bool = False,
-                       q_scale: Optional[torch.Tensor] = None) -> None:
+                       q_scale: Optional[torch.Tensor] = None, conv: Optional[torch.Tensor] = None,
+                       conv_state: Optional[torch.Tensor] = None) -> None:
     """What stands between a QKV product and attention where queries and keys are normalised over all their heads at
     once: per token, in fp32, `q + bias` and `k + bias` are divided by their root mean square over ALL their columns
     and multiplied by `q_norm` / `k_norm` (None: no norm), the leading `rotation.rotary_dim` components of every head
@@ -218,7 +219,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
     serving every head.  `values_from_keys`: qkv holds no values; `k + bias` as projected, before norm and rotation,
     is written as the value (Dv = D).  `qkv` may be the leading columns of a wider matrix (a slice with contiguous
     rows).  `q_scale` (float32 [H]): head h's queries times q_scale[h] after norm and rotation, a factor per head on
-    its scores."""
+    its scores.  `conv` (float32 [taps, columns of qkv], tap-major, the token's own tap last; no bias with it): every
+    column is first convolved over time with the sequence's projected rows before; `conv_state` (float32 [slots + 1,
+    >= (taps - 1) * columns], contiguous rows) holds every sequence's last taps - 1 projected rows, oldest first, and
+    is brought up to date."""
     if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
         raise KernelError("qk_norm_rope_store: qkv must be a matrix with contiguous rows on the device")
     _dev(q_out, "q_out")
@@ -239,6 +243,20 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
     if bias is not None and (bias.dtype != torch.float32 or bias.shape != (cols,) or not bias.is_cuda):
         raise KernelError("qk_norm_rope_store: bias must be float32, one per column of qkv")
     _f32_vec(q_scale, "q_scale", H)
+    taps, lds = 0, 0
+    if conv is not None:
+        _dev(conv, "conv")
+        taps = conv.shape[0]
+        if conv.dtype != torch.float32 or conv.shape != (taps, cols) or bias is not None:
+            raise KernelError(f"qk_norm_rope_store: the convolution's taps must be float32 [taps, {cols}], and no bias with them")
+        if taps > 1:
+            if conv_state is None or not conv_state.is_cuda or conv_state.dtype != torch.float32 or conv_state.dim() != 2 \
+                    or conv_state.stride(1) != 1 or conv_state.shape[1] < (taps - 1) * cols:
+                raise KernelError("qk_norm_rope_store: the convolution needs a float32 state [slots, >= (taps - 1) * columns]")
+            lds = conv_state.stride(0)
+            set_bounds("elementwise", n_seqs=step.n_seqs, device=qkv.device)
+        else:
+            conv_state = None
     for wn, n, size in ((q_norm, "q_norm", D if per_head else H * D), (k_norm if own_kv else None, "k_norm", D if per_head else G * D)):
         if wn is not None and (wn.dtype != q_out.dtype or wn.shape != (size,) or not wn.is_cuda):
             raise KernelError(f"qk_norm_rope_store: {n} must be [{size}] of {q_out.dtype}")
@@ -257,8 +275,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: 
         _p(kv.k) if own_kv else None, _p(kv.v) if own_kv else None, _dt(q_out, "q_out"), _p(cos), _p(sin),
         _p(step.tok_pos), _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, D, Dv, hd_c, rot,
         0 if pairing == "half" else 1, 1 if own_kv else 0, 1 if per_head else 0, 1 if values_from_keys else 0,
-        qkv.stride(0), _p(q_scale), _stream()),
-        f"qk_norm_rope_store T={T}",
+        qkv.stride(0), _p(q_scale), _p(conv), taps, _p(conv_state) if conv is not None else None, lds,
+        _p(step.seq_start) if conv is not None else None, _p(step.seq_slot) if conv is not None else None,
+        step.n_seqs if conv is not None else 0, 1 if conv is not None and step.is_decode else 0, _stream()),
+        f"qk_norm_rope_store T={T}", kernels=2 if conv is not None and taps > 1 and not (step.is_decode and step.n_seqs == T) else 1,
         nbytes=qkv.numel() * qkv.element_size() + T * (H + (2 * G if own_kv else 0)) * hd_c * q_out.element_size())
 
 

@@ -221,12 +221,16 @@ def store_rows_paged(rows: torch.Tensor, pages: torch.Tensor, step, block_table:
 
 
 def latent_store(rows: torch.Tensor, weight: torch.Tensor, eps: float, rotation, n_rot: int, pages: torch.Tensor, step,
-                 block_table: torch.Tensor) -> None:
+                 block_table: torch.Tensor, store: bool = True, q_rows: Optional[torch.Tensor] = None,
+                 q_weight: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """A latent's row into the pages of its cache, made from the projection's columns `rows` [T, n_rot + n_norm]
     (float32 or the run's type; a column slice will do): the first `n_rot` columns rotated by the token's position
     (`rotation`: `ops.Rotation` over n_rot components), the other n_norm divided by their root mean square (`eps`
     inside the root) and multiplied by `weight` (float32 [n_norm]); `pages` [n, 1, PAGE_TOKENS, R] with R >= n_rot +
-    n_norm receive [rotated | normed | zeros] at position tok_pos[t] of sequence tok_seq[t]."""
+    n_norm receive [rotated | normed | zeros] at position tok_pos[t] of sequence tok_seq[t] (`store=False`: nothing
+    is written, for a layer that reads another layer's cache).  On the way the kernel norms a second stretch of the
+    same tokens' rows: `q_rows` [T, n_q] (of rows' type; a column slice will do) divided by its root mean square and
+    multiplied by `q_weight` (float32 [n_q]), returned as [T, n_q] of the pages' type."""
     ld = _cols(rows, "rows")
     _dev(pages, "pages"), _i32(block_table, "block_table")
     T, C = rows.shape
@@ -243,13 +247,23 @@ def latent_store(rows: torch.Tensor, weight: torch.Tensor, eps: float, rotation,
         cos, sin, pairing = rotation.cos, rotation.sin, rotation.pairing
         if step.max_position >= cos.shape[0]:
             raise KernelError(f"position {step.max_position} lies beyond the rotary table")
+    q_out, ldq, n_q = None, 0, 0
+    if q_rows is not None:
+        ldq = _cols(q_rows, "q_rows")
+        n_q = q_rows.shape[1]
+        _f32(q_weight, "q_weight", n_q)
+        if q_rows.shape[0] != T or q_rows.dtype != rows.dtype or q_weight is None:
+            raise KernelError("latent_store: q_rows must be [T, n_q] of rows' type, with a weight")
+        q_out = torch.empty((T, n_q), dtype=pages.dtype, device=rows.device)
     set_bounds("recurrent", n_pages=pages.shape[0], n_seqs=block_table.shape[0],
                n_positions=block_table.shape[1] * PAGE_TOKENS, device=rows.device)
     _check(_fn("recurrent", "plm_latent_store")(
         _p(rows), _dt(rows, "rows"), ld, _p(weight), float(eps), _p(cos), _p(sin), _p(pages), _dt(pages, "pages"),
         _p(step.tok_pos), _p(step.tok_seq), _p(block_table), block_table.shape[1], T, int(n_rot), n_norm, R,
-        0 if pairing == "half" else 1, _stream()), f"latent_store T={T} rot={n_rot} norm={n_norm}",
-        nbytes=T * (C * rows.element_size() + R * pages.element_size()))
+        0 if pairing == "half" else 1, 1 if store else 0, _p(q_rows), ldq, _p(q_weight), _p(q_out), n_q, _stream()),
+        f"latent_store T={T} rot={n_rot} norm={n_norm}",
+        nbytes=T * ((C + n_q) * rows.element_size() + (R + n_q) * pages.element_size()))
+    return q_out
 
 
 def rglru_gates(u: torch.Tensor, w_rate: torch.Tensor, w_in: torch.Tensor, b_rate: torch.Tensor, b_in: torch.Tensor,

@@ -169,7 +169,8 @@ def moe_combine(y: torch.Tensor, pairs: SortedPairs, weights: torch.Tensor, shar
     _check(_fn("routed", "plm_moe_combine")(_p(y), d, _p(pairs.where), _p(weights), top, _p(shared), _p(gate), _p(out), T, d,
                                             _p(ident), _dt(ident, "ident") if ident is not None else 0, _p(add),
                                             float(out_scale), 1 if into is not None else 0,
-                                            _stream()), f"moe_combine T={T} d={d}", nbytes=(top + 2) * T * d * 4)
+                                            _stream()), f"moe_combine T={T} d={d}",
+           nbytes=(top + 1 + (shared is not None) + (add is not None) + (into is not None)) * T * d * 4)
     return out
 
 

@@ -31,6 +31,7 @@ class LatentAttention(Part):
                     rows behind its kv_rank (not normed): one key part that all heads share.  Both are rotated by the
                     position (`position`: a PartSpec of the position family over rot_dim components) and their product
                     is added to the head's score.  The cache keeps the rotated key part in front of the latent.
+      chunk         a mask of chunks of that many positions instead of a window (see `ops.key_mask`)
       sink_name     a tensor [heads]: head h's denominator also holds exp(sink[h])
       gate_per_head True: `W_g` is [heads, hidden] and head h's output is multiplied by sigmoid(W_g h)_h
 
@@ -48,6 +49,9 @@ class LatentAttention(Part):
         self.R, self.Rq, self.scale, self.window = p["kv_rank"], p["q_rank"], float(p["scale"]), p.get("window")
         self.eps = float(p["eps"])
         self.rot = int(p.get("rot_dim") or 0)
+        self.chunk = p.get("chunk")
+        if self.chunk is not None and (self.window is not None or int(self.chunk) <= 0):
+            raise ValueError("a mask of chunks needs a positive size and excludes a sliding window")
         self.sink_name = p.get("sink_name")
         self.gate_per_head = bool(p.get("gate_per_head", False))
         self.position = None
@@ -109,14 +113,15 @@ class LatentAttention(Part):
         rotation = self.position.rotation() if self.position is not None else None
         # norms and the rotation work on the float32 sums where there is a rotated part
         proj = ops.linear(h, self.w_h, torch.float32 if self.rot else dt)
-        c_q = ops.gated_norm(proj[:, :Rq], dt, weight=self.q_norm_w, eps=self.eps)
-        if cache.writable:
-            ops.latent_store(proj[:, Rq:Rq + row], self.c_norm_w, self.eps, rotation, self.rot, cache.k, step, cache.block_table)
+        # the queries' latent is normed by the kernel that makes the cache's row
+        c_q = ops.latent_store(proj[:, Rq:Rq + row], self.c_norm_w, self.eps, rotation, self.rot, cache.k, step, cache.block_table,
+                               store=cache.writable, q_rows=proj[:, :Rq], q_weight=self.q_norm_w)
         q = ops.linear(c_q, self.w_uq, dt)
         q_lat = ops.head_linear(q, self.w_absorb)
         if self.rot:
             ops.rope_rows(q_lat, rotation, step.tok_pos, self.H, self.hd_c)
         latent = KVLayerCache(cache.k, cache.k, cache.block_table, cache.window, cache.writable)
-        o_lat = ops.attention(q_lat.view(h.shape[0], self.H, self.hd_c), latent, step, 1, self.scale, sink=self.sink)
+        o_lat = ops.attention(q_lat.view(h.shape[0], self.H, self.hd_c), latent, step, 1, self.scale, chunk=self.chunk,
+                              sink=self.sink)
         ctx = ops.head_linear(o_lat, self.w_expand, gate=proj[:, Rq + row:], gate_per_head=self.gate_per_head)
         return ops.linear(ctx, self.w_o, torch.float32, defer=True)

@@ -101,8 +101,8 @@ class Attention(Part):
             raise ValueError("attention: a learned sink and a constant one at once")
         self.gate_name, self.head_scale_name = p.get("gate_name"), p.get("head_scale_name")
         self.conv = p.get("conv")
-        if self.conv is not None and (int(self.conv["taps"]) < 1 or self.v_from_k):
-            raise ValueError("attention: a convolution needs at least one tap and values of their own")
+        if self.conv is not None and (int(self.conv["taps"]) < 1 or self.v_from_k or self.bias):
+            raise ValueError("attention: a convolution needs at least one tap, values of their own and projections without bias")
         # the general form: its own kernel between the product and attention, a cache of padded heads
         self.general = (self.vd != self.hd or self.bias or self.qk_norm is not None or not self.own_kv or self.v_from_k
                         or self.sink_name is not None or self.sink_value is not None or self.gate_name is not None
@@ -213,16 +213,14 @@ class Attention(Part):
             raise RuntimeError("a layer that reads another layer's cache must be built with own_kv=False")
         proj = ops.linear(h, self.w_qkv, torch.float32)      # bias, norm and rotation work on the float32 sums
         qkv = proj[:, :self.n_qkv] if self.gate_name is not None else proj
-        if self.w_conv is not None:
-            if self.w_conv.shape[0] > 1 and conv_state is None:
-                raise RuntimeError("attention with a convolution was handed no state for it")
-            state = conv_state.state if conv_state is not None else proj     # (one tap: no state is read)
-            qkv = ops.causal_conv(qkv, self.w_conv, None, state, step, activation=None)
+        if self.w_conv is not None and self.w_conv.shape[0] > 1 and conv_state is None:
+            raise RuntimeError("attention with a convolution was handed no state for it")
         q = torch.empty((h.shape[0], self.H, self.hd_c), dtype=dt, device=h.device)
         rotation = self.position.rotation() if hasattr(self.position, "rotation") else None
         ops.qk_norm_rope_store(qkv, self.b_qkv, self.w_qn, self.w_kn, self.qk_norm["eps"] if self.qk_norm else 0.0, q,
                                cache, rotation, step, self.H, self.G, self.hd, self.vd, own_kv=self.own_kv,
-                               per_head=self.per_head_norm, values_from_keys=self.v_from_k, q_scale=self.head_scale)
+                               per_head=self.per_head_norm, values_from_keys=self.v_from_k, q_scale=self.head_scale,
+                               conv=self.w_conv, conv_state=conv_state.state if conv_state is not None else None)
         ctx = ops.attention(q, cache, step, self.G, self.scale, chunk=self.chunk, sink=self.sink)
         if self.gate_name is not None:
             ctx = ops.gated_norm(ctx, dt, group=self.hd_c, gate=proj[:, self.n_qkv:], gate_mode=ops.GATE_AFTER_NORM,
