@@ -683,7 +683,7 @@ extern "C" int plm_add_bias(float* x, const float* bias, int n_rows, int d, cuda
 __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 __device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
 
-template <typename Ta, typename Tw, typename Tc, int NT>
+template <typename Ta, typename Tw, typename Tc, int NT, bool CONV>
 __global__ void __launch_bounds__(NT)
 qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ bias, const Tw* __restrict__ wq,
                           const Tw* __restrict__ wk, float eps, Tc* __restrict__ q_out, Tc* __restrict__ kc,
@@ -694,7 +694,7 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
                           const float* __restrict__ q_scale, const float* __restrict__ conv_w, int taps,
                           float* __restrict__ conv_state, long state_stride, const int* __restrict__ seq_start,
                           const int* __restrict__ seq_slot, int conv_keeps_state) {
-    extern __shared__ float qk_sm[];                 // [nq + nk]
+    extern __shared__ float qk_sm[];                 // [nq + nk] (with a convolution: [nq + nk + nv])
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -710,13 +710,13 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
     const int n_cols = nq + nk + nv;
     int in_seq = 0;
     float* conv_st = nullptr;
-    if (conv_w) {
+    if (CONV) {
         const int b = PLM_SEQ_NO(tok_seq[t]);
         in_seq = t - seq_start[b];
         conv_st = conv_state + (long)seq_slot[b] * state_stride;
     }
     auto column = [&](int c) -> float {
-        if (!conv_w) return to_f32<Ta>(row[c]);
+        if (!CONV) return to_f32<Ta>(row[c]);
         float acc = 0.f;
         if (taps <= 8) {
             // all taps' inputs asked for at once, then the sum in the same order
@@ -745,6 +745,41 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
         return acc;
     };
     float sq = 0.f, sk = 0.f;
+    const bool batched = CONV && taps <= 4;          // (then the values' columns are convolved here too, into shared memory)
+    if (batched) {
+        // four of a thread's columns at a time: all their taps' inputs are asked for before any is used (a thread's
+        // columns in ascending order, as below, so the sums of squares keep their order)
+        const bool above = in_seq >= taps - 1;       // every input lies in the step's rows above
+        for (int i0 = threadIdx.x; i0 < n_cols; i0 += NT * 4) {
+            float u[4][4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int c = i0 + m * NT;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int back = taps - 1 - j, li = in_seq - back;
+                    u[m][j] = 0.f;
+                    if (c < n_cols && j < taps)
+                        u[m][j] = (above || li >= 0) ? to_f32<Ta>(row[c - (long)back * ld]) : conv_st[(taps - 1 + li) * n_cols + c];
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int c = i0 + m * NT;
+                if (c >= n_cols) continue;
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j < taps) {
+                        acc = fmaf(conv_w[j * n_cols + c], u[m][j], acc);
+                        if (conv_keeps_state && j > 0) conv_st[(j - 1) * n_cols + c] = u[m][j];
+                    }
+                }
+                qk_sm[c] = acc;
+                if (c < nq) sq += acc * acc; else if (c < nq + nk) sk += acc * acc;
+            }
+        }
+    } else
     for (int i = threadIdx.x; i < nq + nk; i += NT) {
         float v = column(i);
         if (bias) v += bias[i];
@@ -828,7 +863,7 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
             if (v_from_k) {
                 if (c < D) v = qk_sm[nq + g * D + c];
             } else if (c < Dv) {
-                v = column(nq + nk + g * Dv + c);
+                v = batched ? qk_sm[nq + nk + g * Dv + c] : column(nq + nk + g * Dv + c);
                 if (bias) v += bias[nq + nk + g * Dv + c];
             }
             vc[((page_base + g) * PLM_PAGE + in_page) * hd_c + c] = from_f32<Tc>(v);
@@ -877,13 +912,13 @@ extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const floa
         (rot_dim & 1))
         return PLM_ERR_SHAPE;
     if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(H * D + (own_kv ? G * D : 0)) * sizeof(float);
+    const size_t smem = (size_t)(conv_w ? conv_cols : H * D + (own_kv ? G * D : 0)) * sizeof(float);
     if (smem > 200 * 1024) return PLM_ERR_SHAPE;
 #define QKN_LAUNCH(Ta_, Tc_)                                                                                           \
     do {                                                                                                               \
         if (smem > 48 * 1024)                                                                                          \
-            cudaFuncSetAttribute(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        cudaError_t e_ = launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
+            cudaFuncSetAttribute(conv_w ? qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256, true> : qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e_ = launch_pdl(conv_w ? qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256, true> : qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256, false>, dim3(n_tokens), dim3(256), smem, stream, \
                                         (const Ta_*)qkv, bias, (const Tc_*)wq, (const Tc_*)wk, eps, (Tc_*)q_out, (Tc_*)kc, \
                                         (Tc_*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table, max_pages, H, G, D, Dv,  \
                                         hd_c, rot_dim, pairing, own_kv, per_head, v_from_k, ld, q_scale, conv_w, taps,  \
@@ -1078,6 +1113,25 @@ extern "C" int plm_rope_rows(void* x, int dtype, long ld, const float* cos_t, co
 // L2 cache as a rule: the price of needing no second pass and no meeting between blocks), unless that token lies in
 // an earlier step.  `state` [slots][d] fp32 keeps each sequence's last unshifted out_a.  The sums run in an order that depends on d only, and the row before is normalised by
 // the same code as the row itself, so a position's result does not depend on how the prompt was cut.
+// Two sums over a block at once (one round of barriers instead of two); each sum's order is that of block_sum.
+template <int NT>
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {      // red: at least 66 floats
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) { red[warp] = a; red[33 + warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        float ta = (lane < NT / 32) ? red[lane] : 0.f, tb = (lane < NT / 32) ? red[33 + lane] : 0.f;
+        ta = warp_sum(ta);
+        tb = warp_sum(tb);
+        if (lane == 0) { red[32] = ta; red[65] = tb; }
+    }
+    __syncthreads();
+    return make_float2(red[32], red[65]);
+}
+
 template <int NT>
 __device__ __forceinline__ float row_sum_squares(const float* __restrict__ row, int d) {
     float ss = 0.f;
@@ -1133,15 +1187,15 @@ norm_pair_shift_kernel(const float* __restrict__ x, const float* __restrict__ w_
     }
 }
 
-// The same with rows whose width is a multiple of 4 and at most 16 * NT: four elements at a time, both rows in registers
-// between the sums of squares and the results, so that x is read once.
-template <typename To, int NT>
+// The same with rows whose width is a multiple of 4 and at most 4 * VPT * NT: four elements at a time, both rows in
+// registers between the sums of squares and the results (VPT float4 a thread and row), so that x is read once.
+template <typename To, int NT, int VPT>
 __global__ void __launch_bounds__(NT)
 norm_pair_shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ w_a, const float* __restrict__ w_b,
                            const float* __restrict__ mix, float* __restrict__ state, long state_stride,
                            const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                            To* __restrict__ out_a, To* __restrict__ out_b, int d, float eps) {
-    __shared__ float red[33];
+    __shared__ float red[66];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -1156,10 +1210,10 @@ norm_pair_shift_vec_kernel(const float* __restrict__ x, const float* __restrict_
     }
     const float* xr = x + (size_t)t * d;
     const float* xo = x + (size_t)(other < 0 ? t : other) * d;
-    float4 v[4], u[4];
+    float4 v[VPT], u[VPT];
     float ss = 0.f, so = 0.f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < VPT; ++k) {
         const int i = (threadIdx.x + k * NT) * 4;
         if (i < d) {
             v[k] = load4(xr + i);
@@ -1170,11 +1224,16 @@ norm_pair_shift_vec_kernel(const float* __restrict__ x, const float* __restrict_
             }
         }
     }
-    const float r = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)d + eps);
-    float ro = r;
-    if (other >= 0) ro = 1.0f / sqrtf(block_sum<NT>(so, red) / (float)d + eps);
+    float r, ro;
+    if (other >= 0) {
+        const float2 sums = block_sum2<NT>(ss, so, red);
+        r = 1.0f / sqrtf(sums.x / (float)d + eps);
+        ro = 1.0f / sqrtf(sums.y / (float)d + eps);
+    } else {
+        r = ro = 1.0f / sqrtf(block_sum<NT>(ss, red) / (float)d + eps);
+    }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < VPT; ++k) {
         const int i = (threadIdx.x + k * NT) * 4;
         if (i >= d) continue;
         const float4 wa = load4(w_a + i);
@@ -1203,12 +1262,18 @@ static int norm_pair_shift_launch(const float* x, const float* w_a, const float*
     const bool aligned = (((uintptr_t)x | (uintptr_t)w_a | (uintptr_t)w_b | (uintptr_t)mix | (uintptr_t)state) & 15) == 0 &&
                          (((uintptr_t)out_a | (uintptr_t)out_b) & 7) == 0 && state_stride % 4 == 0;
     // (which kernel runs, and with it the order of the sums, depends on the row's width and on alignments that a model fixes)
-    if (d % 4 == 0 && aligned && d <= 16 * 256)
-        return plm_status_of(launch_pdl(norm_pair_shift_vec_kernel<To, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
-                                        state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
-    if (d % 4 == 0 && aligned && d <= 16 * 1024)
-        return plm_status_of(launch_pdl(norm_pair_shift_vec_kernel<To, 1024>, dim3(n_tokens), dim3(1024), 0, stream, x, w_a, w_b,
-                                        mix, state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
+    // few registers a thread (VPT) so that many blocks share an SM: what a block waits for is its rows' arrival
+#define NPS_LAUNCH(NT_, VPT_)                                                                                           \
+    return plm_status_of(launch_pdl(norm_pair_shift_vec_kernel<To, NT_, VPT_>, dim3(n_tokens), dim3(NT_), 0, stream, x, w_a,  \
+                                    w_b, mix, state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps))
+    if (d % 4 == 0 && aligned) {
+        if (d <= 4 * 256) NPS_LAUNCH(256, 1);
+        if (d <= 8 * 256) NPS_LAUNCH(256, 2);
+        if (d <= 8 * 512) NPS_LAUNCH(512, 2);
+        if (d <= 8 * 1024) NPS_LAUNCH(1024, 2);
+        if (d <= 16 * 1024) NPS_LAUNCH(1024, 4);
+    }
+#undef NPS_LAUNCH
     return plm_status_of(launch_pdl(norm_pair_shift_kernel<To, 256>, dim3(n_tokens), dim3(256), 0, stream, x, w_a, w_b, mix,
                                     state, state_stride, tok_seq, seq_start, seq_slot, (To*)out_a, (To*)out_b, d, eps));
 }
