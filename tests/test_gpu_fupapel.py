@@ -348,7 +348,7 @@ def test_one_matrix_per_head_with_a_gate_per_head(dtype, T):
     assert (got.double().reshape(T, H, O) - want).abs().max() < (1e-5 if dtype == torch.float32 else 5e-2)
 
 
-@pytest.mark.parametrize("E,ident,top,groups", [(6, 2, 2, (4, 2)), (12, 2, 3, (2, 1)), (5, 0, 1, None), (4, 4, 3, (8, 3)), (7, 1, 8, None)])
+@pytest.mark.parametrize("E,ident,top,groups", [(6, 2, 2, (4, 2)), (10, 2, 3, (3, 1)), (5, 0, 1, None), (4, 4, 3, (8, 3)), (7, 1, 8, None)])
 def test_router_choice_by_softmax_scores(E, ident, top, groups):
     """Softmax over experts and identity experts together, the correction for the choice only (negative choice scores
     included), groups by their best choice score, weights as the scores stand."""
@@ -435,6 +435,34 @@ def test_float32_model_matches_plain_in_every_cut(tmp_path, name):
             _close(got, ref, what=f"batch, request {i}, turn {turn}")
     eng.cache.check()
     assert eng.cache.slots.used == 0
+
+
+def test_few_wanted_rows_and_the_arrangement_without_its_fused_kernels(tmp_path, monkeypatch):
+    """A step of which few rows are wanted narrows the stream in its last layer (with and without a feed-forward there);
+    and the arrangement's general path (norms one after the other, the shift as the part's own convolution, the two
+    sublayers' results joined by a kernel of their own and left pending) gives the same logits as the fused one."""
+    from picolm_b200.parts.block import ParallelNormBlock
+    from picolm_b200.parts.feed_forward import RoutedMLP
+    for name in ("mixed", "odd"):
+        layers, kw = MODELS[name]
+        d, tensors, config = _make(tmp_path, "few" + name, _config(layers, **kw), seed=31)
+        t, u = random_tokens(100, VOCAB, 12), random_tokens(9, VOCAB, 13)
+        want_t, want_u = _plain(tensors, config, t), _plain(tensors, config, u)
+        for general in (False, True):
+            with monkeypatch.context() as m:
+                if general:
+                    m.setattr(ParallelNormBlock, "_fused_norms", lambda self: False)
+                    m.setattr(RoutedMLP, "adds_to_stream", False)
+                eng = _engine(d)
+                a, b = eng.new_sequence(), eng.new_sequence()
+                got = eng.step([(a, t[:70]), (b, u[:5])], [[69, 3], [4]]).float().cpu()
+                _close(got, torch.stack([want_t[69], want_t[3], want_u[4]]), what=f"{name}: three rows of a batch")
+                assert eng.step([(a, t[70:90]), (b, u[5:])], [[], []]) is None
+                got = eng.step([(a, t[90:])], [[9]]).float().cpu()
+                _close(got, want_t[99:100], what=f"{name}: after a step of which nothing was wanted")
+                eng.end_sequence(a), eng.end_sequence(b)
+                if general:
+                    _close(run_tail(eng, t, tail=30), want_t, what=f"{name}: the general path, prompt and single tokens")
 
 
 def test_layer_that_borrows_keys_and_values_keeps_its_own_tails(tmp_path):
@@ -544,16 +572,16 @@ def test_identity_experts_and_the_correction_decide(tmp_path):
 @pytest.mark.parametrize("name", ["wide_heads", "serving"])
 def test_bfloat16_follows_the_plain_implementation(tmp_path, name):
     """The serving precision stays within rounding of the exact logits, and its own cuts agree with each other far
-    more closely than that.  `wide_heads`: head sizes 64 and 128 (the tcgen05 prompt attention); `serving`: 48, 16 and
-    a latent row of 96 (the mma.sync kernels), routed layers whose sizes take the tensor-core products."""
+    more closely than that.  `wide_heads`: head sizes 64 and 128, also for the latent's row (the tcgen05 prompt attention); `serving`: 48, 16 and
+    a latent row of 80 (the mma.sync kernels), routed layers whose sizes take the tensor-core products."""
     if name == "wide_heads":
-        layers = [_attn(heads=4, kv_heads=1, dim=64, vdim=64, rot=16, chunk=120, scale=0.125, mlp=_moe(experts=6, top=2, ff=64)),
-                  _attn2(heads=2, kv_heads=2, dim=128, vdim=128, rot=128, chunk=96, scale=0.09, mlp=_moe(experts=6, top=2, ff=64)),
-                  _latent(heads=4, dim=64, rot_dim=32, vdim=64, kv_rank=96, q_rank=80, scale=0.1, mlp=_moe(experts=6, top=2, ff=64))]
+        layers = [_attn(heads=4, kv_heads=2, dim=64, vdim=64, rot=32, chunk=100, scale=0.11, mlp=_moe(experts=6, top=2, ff=64)),
+                  _attn2(heads=2, kv_heads=2, dim=128, vdim=128, rot=128, chunk=90, scale=0.09, mlp=_moe(experts=6, top=2, ff=64)),
+                  _latent(heads=4, dim=48, rot_dim=32, vdim=80, kv_rank=96, q_rank=72, scale=0.12, mlp=_moe(experts=6, top=2, ff=64))]
     else:
         layers = [_attn(heads=4, kv_heads=2, dim=48, vdim=32, rot=16, chunk=70, scale=0.5, mlp=_moe(experts=6, top=2, ff=64)),
                   _attn2(heads=8, kv_heads=2, dim=16, vdim=16, chunk=33, scale=0.6, mlp=_moe(experts=6, top=2, ff=64)),
-                  _latent(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=64, q_rank=48, scale=0.3, mlp=None),
+                  _latent(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=48, q_rank=40, scale=0.3, mlp=None),
                   _attn2(heads=8, kv_heads=2, dim=16, vdim=16, chunk=100, scale=0.6, kv_from=1, mlp=_moe(experts=6, top=2, ff=64))]
     d, tensors, config = _make(tmp_path, "bf16" + name, _config(layers, width=128), seed=3, std=0.08)
     t, u = random_tokens(200, VOCAB, 5), random_tokens(31, VOCAB, 6)
