@@ -1113,7 +1113,7 @@ extern "C" int plm_rope_rows(void* x, int dtype, long ld, const float* cos_t, co
 // L2 cache as a rule: the price of needing no second pass and no meeting between blocks), unless that token lies in
 // an earlier step.  `state` [slots][d] fp32 keeps each sequence's last unshifted out_a.  The sums run in an order that depends on d only, and the row before is normalised by
 // the same code as the row itself, so a position's result does not depend on how the prompt was cut.
-// Two sums over a block at once (one round of barriers instead of two); each sum's order is that of block_sum.
+// Two sums over a block at once (the barriers of one sum instead of two); each sum's order is that of block_sum.
 template <int NT>
 __device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {      // red: at least 66 floats
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
